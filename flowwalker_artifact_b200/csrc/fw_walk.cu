@@ -1,0 +1,649 @@
+// Random-walk engine for sm_100a: persistent kernel, global atomic query
+// counter, exponential-race reservoir sampler, Philox keyed by (query, step).
+//
+// Stands in for the reference's production scheduler kernels
+// (include/walker.cuh:1307-1442 and 1444-1580), its warp/block samplers
+// (include/sampler.cuh:46-200), the four walker classes (include/app.cuh:58-152),
+// the per-query Task (include/gpu_task.cuh:24-78), the XORWOW stream
+// (include/myrand.cuh) and the host launch slice (src/walk.cu:373-466, 527-649).
+//
+// Sampling law per step: P(edge i) = bias_i / sum(bias), as the reference's
+// prefix-sum reservoir gives (include/sampler.cuh:46-85).  Mechanism: each
+// candidate group draws key = E / W (E exponential from Philox, W the group's
+// total bias); the smallest (key, group id) wins.  min is associative and
+// commutative, so the result does not depend on which lane, warp or CTA
+// looked at which part of the row, and a CPU walker using the same stream
+// reproduces every walk bit for bit.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <new>
+
+#include "fw_internal.h"
+#include "fw_spec.cuh"
+
+namespace {
+
+constexpr int kMaxSchema = 64;
+constexpr int kThreads = 256;  // 8 warps per CTA
+constexpr int kClaim = 4;      // queries claimed per atomic
+constexpr int kMaxSmemHist = 8192;
+
+// Scratch words (uint64) in device memory.
+constexpr int kSlotSteps = 0, kSlotScanned = 1, kSlotStatus = 2, kSlotCounter = 3, kSlotHist = 4;
+
+struct WalkArgs {
+  const void* xadj;
+  const int32_t* adj;
+  const float* weight;
+  const int32_t* label;
+  int64_t V;
+  const int32_t* starts;
+  int64_t n;
+  int32_t* result;
+  unsigned long long* scratch;
+  uint64_t qid_base;
+  int32_t d;
+  uint32_t tp_thresh;
+  float inv_p, inv_q;
+  uint32_t k0, k1;
+  int32_t hist_in_smem;
+  int32_t schema_len;
+  int32_t schema[kMaxSchema];
+};
+
+struct Row {
+  int64_t b, e;  // absolute edge range
+};
+
+// Per-step context handed to the bias loaders.
+struct StepCtx {
+  int64_t q0;     // b >> 2
+  uint32_t nq;    // quads in the row
+  uint32_t head;  // b - 4*q0
+  uint32_t tail;  // e - 4*q0
+  int32_t prev;   // previous vertex or -1
+  int64_t pb, pe; // row of prev (node2vec)
+  int32_t want;   // label wanted (MetaPath)
+};
+
+__device__ __forceinline__ float pos(float x) { return fmaxf(x, 0.0f); }
+
+// include/gpu_graph.cuh:97-118: membership of `target` in a sorted row.
+__device__ __forceinline__ bool row_contains(const int32_t* __restrict__ adj, int64_t lo, int64_t hi,
+                                             int32_t target) {
+  --hi;
+  while (lo <= hi) {
+    const int64_t mid = lo + ((hi - lo) >> 1);
+    const int32_t a = __ldg(adj + mid);
+    if (a == target) return true;
+    if (a < target) lo = mid + 1; else hi = mid - 1;
+  }
+  return false;
+}
+
+// Biases of the four edges of quad q (0 for edges outside the row and for
+// non-positive or NaN biases).
+template <int APP>
+__device__ __forceinline__ float4 load_bias4(const WalkArgs& a, const StepCtx& c, uint32_t q) {
+  float4 v;
+  if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
+    const int4 l = __ldg(reinterpret_cast<const int4*>(a.label) + (c.q0 + q));
+    v.x = l.x == c.want ? 1.0f : 0.0f;
+    v.y = l.y == c.want ? 1.0f : 0.0f;
+    v.z = l.z == c.want ? 1.0f : 0.0f;
+    v.w = l.w == c.want ? 1.0f : 0.0f;
+  } else {
+    v = __ldg(reinterpret_cast<const float4*>(a.weight) + (c.q0 + q));
+    if (APP == FW_APP_NODE2VEC && c.prev >= 0) {  // include/app.cuh:109-122
+      const int4 x = __ldg(reinterpret_cast<const int4*>(a.adj) + (c.q0 + q));
+      const int32_t xs[4] = {x.x, x.y, x.z, x.w};
+      float* vs = &v.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t r = 4u * q + k;
+        if (r < c.head || r >= c.tail) continue;
+        if (xs[k] == c.prev) vs[k] = __fmul_rn(vs[k], a.inv_p);
+        else if (!row_contains(a.adj, c.pb, c.pe, xs[k])) vs[k] = __fmul_rn(vs[k], a.inv_q);
+      }
+    }
+    v.x = pos(v.x); v.y = pos(v.y); v.z = pos(v.z); v.w = pos(v.w);
+  }
+  if (q == 0 || q + 1 == c.nq) {
+    const uint32_t r = 4u * q;
+    if (r + 0 < c.head || r + 0 >= c.tail) v.x = 0.0f;
+    if (r + 1 < c.head || r + 1 >= c.tail) v.y = 0.0f;
+    if (r + 2 < c.head || r + 2 >= c.tail) v.z = 0.0f;
+    if (r + 3 < c.head || r + 3 >= c.tail) v.w = 0.0f;
+  }
+  return v;
+}
+
+__device__ __forceinline__ float sum4(const float4 v) {
+  return __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w));
+}
+
+// Smallest (key, id) over the warp; ids are unique.
+__device__ __forceinline__ void warp_argmin(uint32_t& key, uint32_t& id) {
+  const uint32_t m = __reduce_min_sync(0xFFFFFFFFu, key);
+  id = __reduce_min_sync(0xFFFFFFFFu, key == m ? id : 0xFFFFFFFFu);
+  key = m;
+}
+
+// One weighted pick in the row described by c, by one warp.  Returns the
+// absolute edge index, or -1 when no edge has positive bias.
+template <int APP, int MODE>
+__device__ __forceinline__ int64_t sample_row_warp(const WalkArgs& a, const StepCtx& c, uint32_t c1,
+                                                   uint32_t qlo, uint32_t qhi, int lane) {
+  uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu;
+  if (MODE == FW_GROUP_EDGE) {
+    for (uint32_t q = lane; q < c.nq; q += 32) {
+      const float4 v = load_bias4<APP>(a, c, q);
+      const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.k0, a.k1);
+      const float vs[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t rs[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (vs[k] > 0.0f) {
+          const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(rs[k]), vs[k]));
+          if (bits < best_key) { best_key = bits; best_id = 4u * q + k; }
+        }
+      }
+    }
+    warp_argmin(best_key, best_id);
+    if (best_id == 0xFFFFFFFFu) return -1;
+    return 4 * c.q0 + (int64_t)best_id;
+  }
+  // strips
+  const uint32_t nsuper = (c.nq + fw::kQuadsPerSuper - 1) / fw::kQuadsPerSuper;
+  for (uint32_t s = 0; s < nsuper; ++s) {
+    const uint32_t base = s * fw::kQuadsPerSuper + lane;
+    float S[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t q = base + 32u * j;
+      S[j] = q < c.nq ? sum4(load_bias4<APP>(a, c, q)) : 0.0f;
+    }
+    const float W = __fadd_rn(__fadd_rn(S[0], S[1]), __fadd_rn(S[2], S[3]));
+    if (W > 0.0f) {
+      const uint32_t B = s * 32u + lane;
+      const fw::Philox4 r = fw::philox4x32_10(B, c1, qlo, qhi, a.k0, a.k1);
+      const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(r.x), W));
+      if (bits < best_key) { best_key = bits; best_id = B; }
+    }
+  }
+  warp_argmin(best_key, best_id);
+  if (best_id == 0xFFFFFFFFu) return -1;
+  // inverse-CDF pick inside the winning strip (every lane computes the same)
+  const uint32_t B = best_id;
+  const uint32_t qb = (B >> 5) * fw::kQuadsPerSuper + (B & 31u);
+  const fw::Philox4 r = fw::philox4x32_10(B, c1, qlo, qhi, a.k0, a.k1);
+  float4 v[4];
+  float S[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t q = qb + 32u * j;
+    v[j] = q < c.nq ? load_bias4<APP>(a, c, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[j] = sum4(v[j]);
+  }
+  const float W = __fadd_rn(__fadd_rn(S[0], S[1]), __fadd_rn(S[2], S[3]));
+  const float t = __fmul_rn((float)(r.y >> 8) * 0x1p-24f, W);
+  float acc = 0.0f;
+  int64_t last = -1, chosen = -1;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (vs[k] > 0.0f && chosen < 0) {
+        last = 4 * (c.q0 + qb + 32u * j) + k;
+        acc = __fadd_rn(acc, vs[k]);
+        if (acc > t) chosen = last;
+      }
+    }
+  }
+  return chosen >= 0 ? chosen : last;
+}
+
+template <int APP, int MODE, typename OffT>
+__global__ void __launch_bounds__(kThreads) walk_kernel(const __grid_constant__ WalkArgs a) {
+  extern __shared__ uint32_t s_hist[];
+  const int lane = threadIdx.x & 31;
+  const OffT* __restrict__ xadj = static_cast<const OffT*>(a.xadj);
+  const int64_t D = (int64_t)a.d + 1;
+  if (a.hist_in_smem) {
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x) s_hist[z] = 0u;
+    __syncthreads();
+  }
+  unsigned long long my_steps = 0, my_scanned = 0;
+  uint32_t status = 0;
+
+  for (;;) {
+    long long first = 0;
+    if (lane == 0) first = (long long)atomicAdd(a.scratch + kSlotCounter, (unsigned long long)kClaim);
+    first = __shfl_sync(0xFFFFFFFFu, first, 0);
+    if (first >= a.n) break;
+    const long long stop = first + kClaim < a.n ? first + kClaim : a.n;
+    for (long long qi = first; qi < stop; ++qi) {
+      const uint64_t qid = a.qid_base + (uint64_t)qi;
+      const uint32_t qlo = (uint32_t)qid, qhi = (uint32_t)(qid >> 32);
+      int32_t* __restrict__ row_out = a.result + qi * D;
+      int32_t cur = __ldg(a.starts + qi);
+      if (lane == 0) row_out[0] = cur;
+      StepCtx c;
+      c.prev = -1; c.pb = 0; c.pe = 0; c.want = 0;
+      int k = 0;
+      if (cur < 0 || (int64_t)cur >= a.V) {
+        status |= FW_STATUS_BAD_START;
+      } else {
+        while (k < a.d) {
+          const int64_t b = (int64_t)__ldg(xadj + cur), e = (int64_t)__ldg(xadj + cur + 1);
+          if (e <= b) break;
+          c.q0 = b >> 2;
+          c.nq = (uint32_t)(((e + 3) >> 2) - c.q0);
+          c.head = (uint32_t)(b - 4 * c.q0);
+          c.tail = (uint32_t)(e - 4 * c.q0);
+          if (APP == FW_APP_METAPATH) c.want = a.schema[k % a.schema_len];
+          const int64_t sel = sample_row_warp<APP, MODE>(a, c, (uint32_t)k | (fw::kPurposeScan << 28),
+                                                         qlo, qhi, lane);
+          if (sel < 0) break;  // include/walker.cuh:1373-1374
+          const int32_t nxt = __ldg(a.adj + sel);
+          if (nxt < 0 || (int64_t)nxt >= a.V) { status |= FW_STATUS_BAD_NEIGHBOR; break; }
+          if (lane == 0) row_out[k + 1] = nxt;  // include/walker.cuh:1380-1381
+          my_scanned += (unsigned long long)(e - b);
+          c.prev = cur; c.pb = b; c.pe = e;  // include/gpu_task.cuh:70-77
+          cur = nxt;
+          ++k;
+          if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
+            const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(k - 1) | (fw::kPurposeStop << 28),
+                                                    qlo, qhi, a.k0, a.k1);
+            if (r.x < a.tp_thresh) break;
+          }
+        }
+      }
+      for (int z = k + 1 + lane; z <= a.d; z += 32) row_out[z] = -1;
+      my_steps += (unsigned long long)k;
+      if (lane == 0) {
+        if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
+        else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+      }
+    }
+  }
+  if (lane == 0) {
+    if (my_steps) atomicAdd(a.scratch + kSlotSteps, my_steps);
+    if (my_scanned) atomicAdd(a.scratch + kSlotScanned, my_scanned);
+    if (status) atomicOr(a.scratch + kSlotStatus, (unsigned long long)status);
+  }
+  if (a.hist_in_smem) {
+    __syncthreads();
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x)
+      if (s_hist[z]) atomicAdd(a.scratch + kSlotHist + z, (unsigned long long)s_hist[z]);
+  }
+}
+
+using KernelFn = void (*)(const WalkArgs);
+
+template <int APP, int MODE>
+KernelFn pick_off(int xadj_bits) {
+  return xadj_bits == 64 ? (KernelFn)walk_kernel<APP, MODE, int64_t>
+                         : (KernelFn)walk_kernel<APP, MODE, uint32_t>;
+}
+template <int APP>
+KernelFn pick_mode(int mode, int xadj_bits) {
+  return mode == FW_GROUP_EDGE ? pick_off<APP, FW_GROUP_EDGE>(xadj_bits)
+                               : pick_off<APP, FW_GROUP_STRIP>(xadj_bits);
+}
+KernelFn pick_kernel(int app, int mode, int xadj_bits) {
+  switch (app) {
+    case FW_APP_DEEPWALK: return pick_mode<FW_APP_DEEPWALK>(mode, xadj_bits);
+    case FW_APP_PPR: return pick_mode<FW_APP_PPR>(mode, xadj_bits);
+    case FW_APP_NODE2VEC: return pick_mode<FW_APP_NODE2VEC>(mode, xadj_bits);
+    default: return pick_mode<FW_APP_METAPATH>(mode, xadj_bits);
+  }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Engine
+// ---------------------------------------------------------------------------
+
+struct fw_engine {
+  int device = 0;
+  int sms = 0;
+  int64_t V = 0, E = 0;
+  int xadj_bits = 32;
+  void* d_xadj = nullptr;
+  int32_t* d_adj = nullptr;
+  float* d_weight = nullptr;
+  int32_t* d_label = nullptr;
+  unsigned long long* d_scratch = nullptr;  // counters + histogram
+  unsigned long long* h_scratch = nullptr;  // pinned mirror
+  size_t scratch_words = 0;
+  cudaStream_t stream = nullptr, stream2 = nullptr;
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  // staging for the host-buffer entry points (grown on demand)
+  int32_t* d_starts[2] = {nullptr, nullptr};
+  int32_t* d_result[2] = {nullptr, nullptr};
+  size_t cap_starts[2] = {0, 0}, cap_result[2] = {0, 0};
+};
+
+namespace {
+
+#define FW_CUDA(call)                                                                   \
+  do {                                                                                  \
+    cudaError_t err__ = (call);                                                         \
+    if (err__ != cudaSuccess)                                                           \
+      return fw::fail(FW_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(err__));  \
+  } while (0)
+
+struct DeviceGuard {
+  int prev = 0;
+  explicit DeviceGuard(int dev) { cudaGetDevice(&prev); cudaSetDevice(dev); }
+  ~DeviceGuard() { cudaSetDevice(prev); }
+};
+
+// Edge arrays are padded to whole quads (plus one) so that 16-byte loads of
+// the first and last quad of any row stay inside the allocation.
+template <typename T>
+int upload_edges(const T* host, int64_t E, T** out) {
+  const size_t padded = ((size_t)E + 3) / 4 * 4 + 4;
+  FW_CUDA(cudaMalloc(out, padded * sizeof(T)));
+  FW_CUDA(cudaMemset(*out, 0, padded * sizeof(T)));
+  if (E > 0) FW_CUDA(cudaMemcpy(*out, host, (size_t)E * sizeof(T), cudaMemcpyHostToDevice));
+  return FW_OK;
+}
+
+int ensure_scratch(fw_engine* e, int d) {
+  const size_t words = (size_t)kSlotHist + (size_t)d + 1;
+  if (words <= e->scratch_words) return FW_OK;
+  if (e->d_scratch) cudaFree(e->d_scratch);
+  if (e->h_scratch) cudaFreeHost(e->h_scratch);
+  e->d_scratch = nullptr; e->h_scratch = nullptr; e->scratch_words = 0;
+  const size_t cap = std::max<size_t>(words, 1024);
+  FW_CUDA(cudaMalloc(&e->d_scratch, cap * 8));
+  FW_CUDA(cudaMallocHost(&e->h_scratch, cap * 8));
+  e->scratch_words = cap;
+  return FW_OK;
+}
+
+int check_params(const fw_engine* e, const fw_walk_params* p, int64_t n) {
+  if (!e || !p) return fw::fail(FW_ERR_ARG, "null engine or params");
+  if (n < 0) return fw::fail(FW_ERR_ARG, "negative query count");
+  if (p->app < FW_APP_DEEPWALK || p->app > FW_APP_METAPATH) return fw::fail(FW_ERR_ARG, "unknown app %d", p->app);
+  if (p->d < 0 || p->d >= (1 << 28)) return fw::fail(FW_ERR_ARG, "d out of range");
+  if (p->group_mode != 0 && p->group_mode != FW_GROUP_EDGE && p->group_mode != FW_GROUP_STRIP)
+    return fw::fail(FW_ERR_ARG, "group_mode must be 0, %d or %d", FW_GROUP_EDGE, FW_GROUP_STRIP);
+  if (p->app == FW_APP_METAPATH) {
+    if (!e->d_label) return fw::fail(FW_ERR_ARG, "MetaPath needs edge labels on the device");
+    if (!p->schema || p->schema_len <= 0 || p->schema_len > kMaxSchema)
+      return fw::fail(FW_ERR_ARG, "schema length must be in 1..%d", kMaxSchema);
+  } else if (!e->d_weight) {
+    return fw::fail(FW_ERR_ARG, "this app needs edge weights on the device");
+  }
+  if (p->app == FW_APP_NODE2VEC && !(p->p > 0.0 && p->q > 0.0))
+    return fw::fail(FW_ERR_ARG, "node2vec needs p > 0 and q > 0");
+  return FW_OK;
+}
+
+// Enqueues: scratch reset, kernel between ev[0] and ev[1], scratch read-back.
+int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_dev, int64_t n,
+                 int32_t* result_dev, cudaStream_t st, cudaEvent_t ev_begin, cudaEvent_t ev_end,
+                 unsigned long long* d_scratch, unsigned long long* h_scratch) {
+  WalkArgs a;
+  a.xadj = e->d_xadj; a.adj = e->d_adj; a.weight = e->d_weight; a.label = e->d_label;
+  a.V = e->V; a.starts = starts_dev; a.n = n; a.result = result_dev; a.scratch = d_scratch;
+  a.qid_base = p->query_id_base; a.d = p->d;
+  a.tp_thresh = fw::tp_threshold(p->tp);
+  a.inv_p = (float)(1.0 / p->p); a.inv_q = (float)(1.0 / p->q);
+  a.k0 = (uint32_t)p->seed; a.k1 = (uint32_t)(p->seed >> 32);
+  a.hist_in_smem = p->d + 1 <= kMaxSmemHist;
+  a.schema_len = p->app == FW_APP_METAPATH ? p->schema_len : 1;
+  for (int i = 0; i < kMaxSchema; ++i) a.schema[i] = (p->app == FW_APP_METAPATH && i < p->schema_len) ? p->schema[i] : 0;
+  const int mode = p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode;
+  KernelFn fn = pick_kernel(p->app, mode, e->xadj_bits);
+  const size_t smem = a.hist_in_smem ? (size_t)(p->d + 1) * 4 : 0;
+  int per_sm = 0;
+  FW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
+  if (per_sm < 1) return fw::fail(FW_ERR_CUDA, "walk kernel does not fit on an SM");
+  const size_t words = (size_t)kSlotHist + (size_t)p->d + 1;
+  FW_CUDA(cudaMemsetAsync(d_scratch, 0, words * 8, st));
+  FW_CUDA(cudaEventRecord(ev_begin, st));
+  if (n > 0) {
+    const int64_t want = (n + (kThreads / 32) * kClaim - 1) / ((kThreads / 32) * kClaim);
+    const int grid = (int)std::min<int64_t>((int64_t)e->sms * per_sm, std::max<int64_t>(want, 1));
+    void* params[] = {&a};
+    FW_CUDA(cudaLaunchKernel((const void*)fn, dim3(grid), dim3(kThreads), params, smem, st));
+  }
+  FW_CUDA(cudaEventRecord(ev_end, st));
+  FW_CUDA(cudaMemcpyAsync(h_scratch, d_scratch, words * 8, cudaMemcpyDeviceToHost, st));
+  return FW_OK;
+}
+
+void collect(const unsigned long long* h, int d, float ms, int launches, fw_walk_stats* stats,
+             uint64_t* len_hist, bool accumulate) {
+  if (stats) {
+    if (!accumulate) { stats->steps = 0; stats->scanned = 0; stats->device_ms = 0; stats->device_status = 0; stats->launches = 0; }
+    stats->steps += h[kSlotSteps];
+    stats->scanned += h[kSlotScanned];
+    stats->device_status |= (uint32_t)h[kSlotStatus];
+    stats->device_ms += ms;
+    stats->launches += (uint32_t)launches;
+  }
+  if (len_hist)
+    for (int z = 0; z <= d; ++z) len_hist[z] = (accumulate ? len_hist[z] : 0) + h[kSlotHist + z];
+}
+
+template <typename T>
+int ensure_cap(T** buf, size_t* cap, size_t need) {
+  if (need <= *cap) return FW_OK;
+  if (*buf) cudaFree(*buf);
+  *buf = nullptr; *cap = 0;
+  cudaError_t err = cudaMalloc(buf, std::max<size_t>(need, 1) * sizeof(T));
+  if (err != cudaSuccess)
+    return fw::fail(FW_ERR_NOMEM, "cudaMalloc of %zu bytes failed: %s", need * sizeof(T), cudaGetErrorString(err));
+  *cap = need;
+  return FW_OK;
+}
+
+}  // namespace
+
+extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_engine** out) {
+  fw::clear_error();
+  if (!g || !out) return fw::fail(FW_ERR_ARG, "fw_engine_create: null argument");
+  *out = nullptr;
+  int count = 0;
+  FW_CUDA(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count) return fw::fail(FW_ERR_ARG, "device %d out of range (%d visible)", device, count);
+  DeviceGuard guard(device);
+  cudaDeviceProp prop;
+  FW_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major < 10) return fw::fail(FW_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+  fw_engine* e = new (std::nothrow) fw_engine();
+  if (!e) return fw::fail(FW_ERR_NOMEM, "out of host memory");
+  e->device = device; e->sms = prop.multiProcessorCount;
+  e->V = g->V; e->E = g->E; e->xadj_bits = g->xadj_bits;
+  const bool want_w = which == 0 ? g->weight != nullptr : (which & 1) != 0;
+  const bool want_l = which == 0 ? g->label != nullptr : (which & 2) != 0;
+  int rc = FW_OK;
+  auto body = [&]() -> int {
+    if (want_w && !g->weight) return fw::fail(FW_ERR_ARG, "graph has no weights");
+    if (want_l && !g->label) return fw::fail(FW_ERR_ARG, "graph has no labels");
+    const size_t xb = (size_t)(g->xadj_bits / 8) * (size_t)(g->V + 2);
+    FW_CUDA(cudaMalloc(&e->d_xadj, xb));
+    FW_CUDA(cudaMemcpy(e->d_xadj, g->xadj, (size_t)(g->xadj_bits / 8) * (size_t)(g->V + 1), cudaMemcpyHostToDevice));
+    int r = upload_edges(g->adj, g->E, &e->d_adj);
+    if (!r && want_w) r = upload_edges(g->weight, g->E, &e->d_weight);
+    if (!r && want_l) r = upload_edges(g->label, g->E, &e->d_label);
+    if (r) return r;
+    FW_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    FW_CUDA(cudaStreamCreateWithFlags(&e->stream2, cudaStreamNonBlocking));
+    for (auto& ev : e->ev) FW_CUDA(cudaEventCreate(&ev));
+    return ensure_scratch(e, 1023);
+  };
+  rc = body();
+  if (rc) { fw_engine_destroy(e); return rc; }
+  *out = e;
+  return FW_OK;
+}
+
+extern "C" void fw_engine_destroy(fw_engine* e) {
+  if (!e) return;
+  DeviceGuard guard(e->device);
+  cudaFree(e->d_xadj); cudaFree(e->d_adj); cudaFree(e->d_weight); cudaFree(e->d_label);
+  cudaFree(e->d_scratch);
+  if (e->h_scratch) cudaFreeHost(e->h_scratch);
+  for (int i = 0; i < 2; ++i) { cudaFree(e->d_starts[i]); cudaFree(e->d_result[i]); }
+  if (e->stream) cudaStreamDestroy(e->stream);
+  if (e->stream2) cudaStreamDestroy(e->stream2);
+  for (auto& ev : e->ev) if (ev) cudaEventDestroy(ev);
+  delete e;
+}
+
+extern "C" int fw_engine_device(const fw_engine* e, int* device, int* sm_count) {
+  if (!e) return fw::fail(FW_ERR_ARG, "fw_engine_device: null engine");
+  if (device) *device = e->device;
+  if (sm_count) *sm_count = e->sms;
+  return FW_OK;
+}
+
+extern "C" int fw_walk_device(fw_engine* e, const fw_walk_params* p, const int32_t* starts_dev,
+                              int64_t n, int32_t* result_dev, void* stream, fw_walk_stats* stats,
+                              uint64_t* len_hist) {
+  fw::clear_error();
+  int rc = check_params(e, p, n);
+  if (rc) return rc;
+  if (n > 0 && (!starts_dev || !result_dev)) return fw::fail(FW_ERR_ARG, "null device buffer");
+  DeviceGuard guard(e->device);
+  rc = ensure_scratch(e, p->d);
+  if (rc) return rc;
+  cudaStream_t st = stream ? (cudaStream_t)stream : e->stream;
+  rc = enqueue_walk(e, p, starts_dev, n, result_dev, st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch);
+  if (rc) return rc;
+  FW_CUDA(cudaStreamSynchronize(st));
+  float ms = 0.f;
+  FW_CUDA(cudaEventElapsedTime(&ms, e->ev[0], e->ev[1]));
+  collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
+  if (stats) stats->total_ms = ms;
+  return FW_OK;
+}
+
+extern "C" int fw_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_host, int64_t n,
+                       int32_t* result_host, fw_walk_stats* stats, uint64_t* len_hist) {
+  fw::clear_error();
+  int rc = check_params(e, p, n);
+  if (rc) return rc;
+  if (n > 0 && (!starts_host || !result_host)) return fw::fail(FW_ERR_ARG, "null host buffer");
+  DeviceGuard guard(e->device);
+  rc = ensure_scratch(e, p->d);
+  if (rc) return rc;
+  const size_t cells = (size_t)n * (size_t)(p->d + 1);
+  rc = ensure_cap(&e->d_starts[0], &e->cap_starts[0], (size_t)n);
+  if (!rc) rc = ensure_cap(&e->d_result[0], &e->cap_result[0], cells);
+  if (rc) return rc;
+  cudaStream_t st = e->stream;
+  FW_CUDA(cudaEventRecord(e->ev[2], st));
+  if (n > 0) FW_CUDA(cudaMemcpyAsync(e->d_starts[0], starts_host, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+  rc = enqueue_walk(e, p, e->d_starts[0], n, e->d_result[0], st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch);
+  if (rc) return rc;
+  if (n > 0) FW_CUDA(cudaMemcpyAsync(result_host, e->d_result[0], cells * 4, cudaMemcpyDeviceToHost, st));
+  FW_CUDA(cudaEventRecord(e->ev[3], st));
+  FW_CUDA(cudaStreamSynchronize(st));
+  float ms = 0.f, total = 0.f;
+  FW_CUDA(cudaEventElapsedTime(&ms, e->ev[0], e->ev[1]));
+  FW_CUDA(cudaEventElapsedTime(&total, e->ev[2], e->ev[3]));
+  collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
+  if (stats) stats->total_ms = total;
+  return FW_OK;
+}
+
+extern "C" void fw_free_pinned(void* p) {
+  if (p) cudaFreeHost(p);
+}
+
+// walk_batch: two streams, double-buffered batches (src/walk.cu:373-466).
+extern "C" int fw_walk_batch(fw_engine* e, const fw_walk_params* p, const int32_t* starts_host,
+                             int64_t n, int64_t batch_size, int32_t headroom_mb,
+                             int32_t** result_pinned, fw_walk_stats* stats, uint64_t* len_hist) {
+  fw::clear_error();
+  int rc = check_params(e, p, n);
+  if (rc) return rc;
+  if (!result_pinned || (n > 0 && !starts_host)) return fw::fail(FW_ERR_ARG, "null buffer");
+  *result_pinned = nullptr;
+  DeviceGuard guard(e->device);
+  const size_t D = (size_t)p->d + 1;
+  if (batch_size <= 0) {  // --autobatch, src/main.cu:259-271
+    size_t free_b = 0, total_b = 0;
+    FW_CUDA(cudaMemGetInfo(&free_b, &total_b));
+    for (int i = 0; i < 2; ++i) free_b += e->cap_starts[i] * 4 + e->cap_result[i] * 4;
+    const size_t head = (size_t)std::max(headroom_mb, 0) << 20;
+    if (free_b <= head) return fw::fail(FW_ERR_NOMEM, "no device memory left after %d MB headroom", headroom_mb);
+    batch_size = (int64_t)std::min<size_t>((free_b - head) / (4 * (D + 1)) / 2, (size_t)INT32_MAX);
+    if (batch_size < 1) return fw::fail(FW_ERR_NOMEM, "device memory too small for one query");
+  }
+  batch_size = std::max<int64_t>(1, std::min(batch_size, std::max<int64_t>(n, 1)));
+  // second scratch block for the second stream lives behind the first
+  const size_t words = (size_t)kSlotHist + D;
+  rc = ensure_scratch(e, (int)(2 * words));
+  if (rc) return rc;
+  int32_t* pinned = nullptr;
+  {
+    cudaError_t err = cudaMallocHost(&pinned, std::max<size_t>((size_t)n * D * 4, 4));
+    if (err != cudaSuccess) return fw::fail(FW_ERR_NOMEM, "cudaMallocHost failed: %s", cudaGetErrorString(err));
+  }
+  auto bail = [&](int code) { cudaStreamSynchronize(e->stream); cudaStreamSynchronize(e->stream2); cudaFreeHost(pinned); return code; };
+  for (int i = 0; i < 2; ++i) {
+    rc = ensure_cap(&e->d_starts[i], &e->cap_starts[i], (size_t)batch_size);
+    if (!rc) rc = ensure_cap(&e->d_result[i], &e->cap_result[i], (size_t)batch_size * D);
+    if (rc) return bail(rc);
+  }
+  cudaStream_t streams[2] = {e->stream, e->stream2};
+  cudaEvent_t evs[2][2] = {{e->ev[0], e->ev[1]}, {e->ev[2], e->ev[3]}};
+  unsigned long long* dsc[2] = {e->d_scratch, e->d_scratch + words};
+  unsigned long long* hsc[2] = {e->h_scratch, e->h_scratch + words};
+  if (stats) { stats->steps = 0; stats->scanned = 0; stats->device_ms = 0; stats->total_ms = 0; stats->device_status = 0; stats->launches = 0; }
+  if (len_hist) for (size_t z = 0; z < D; ++z) len_hist[z] = 0;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  if (cudaEventCreate(&t0) != cudaSuccess || cudaEventCreate(&t1) != cudaSuccess)
+    return bail(fw::fail(FW_ERR_CUDA, "cudaEventCreate failed"));
+  cudaEventRecord(t0, streams[0]);
+  bool pending[2] = {false, false};
+  auto drain = [&](int s) -> int {
+    if (!pending[s]) return FW_OK;
+    FW_CUDA(cudaStreamSynchronize(streams[s]));
+    float ms = 0.f;
+    FW_CUDA(cudaEventElapsedTime(&ms, evs[s][0], evs[s][1]));
+    collect(hsc[s], p->d, ms, 1, stats, len_hist, true);
+    pending[s] = false;
+    return FW_OK;
+  };
+  int which = 0;
+  fw_walk_params bp = *p;
+  for (int64_t off = 0; off < n && !rc; off += batch_size, which ^= 1) {
+    const int64_t m = std::min(batch_size, n - off);
+    rc = drain(which);
+    if (rc) break;
+    cudaStream_t st = streams[which];
+    bp.query_id_base = p->query_id_base + (uint64_t)off;
+    cudaError_t err = cudaMemcpyAsync(e->d_starts[which], starts_host + off, (size_t)m * 4, cudaMemcpyHostToDevice, st);
+    if (err != cudaSuccess) { rc = fw::fail(FW_ERR_CUDA, "H2D copy failed: %s", cudaGetErrorString(err)); break; }
+    rc = enqueue_walk(e, &bp, e->d_starts[which], m, e->d_result[which], st, evs[which][0], evs[which][1], dsc[which], hsc[which]);
+    if (rc) break;
+    err = cudaMemcpyAsync(pinned + (size_t)off * D, e->d_result[which], (size_t)m * D * 4, cudaMemcpyDeviceToHost, st);
+    if (err != cudaSuccess) { rc = fw::fail(FW_ERR_CUDA, "D2H copy failed: %s", cudaGetErrorString(err)); break; }
+    pending[which] = true;
+  }
+  if (!rc) rc = drain(0);
+  if (!rc) rc = drain(1);
+  if (!rc) {
+    cudaEventRecord(t1, streams[0]);
+    cudaEventSynchronize(t1);
+    float total = 0.f;
+    cudaEventElapsedTime(&total, t0, t1);
+    if (stats) stats->total_ms = total;
+  }
+  cudaEventDestroy(t0); cudaEventDestroy(t1);
+  if (rc) return bail(rc);
+  *result_pinned = pinned;
+  return FW_OK;
+}

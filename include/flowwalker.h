@@ -1,0 +1,165 @@
+/*
+ * flowwalker.h -- C ABI of the B200 random-walk engine.
+ *
+ * Plain C types only: pointers, sizes and PODs.  Every function returns an
+ * int status (FW_OK = 0, negative = error; the message is available from
+ * fw_last_error() on the calling thread) and never calls exit().  Objects
+ * created by a *_create / *_load / *_generate call are released by the matching
+ * *_destroy.  Buffers passed in stay owned by the caller.
+ *
+ * The reference program has no FFI of its own; its operator surface for the
+ * walk path is (a) the on-disk CSR format, (b) the two host entry points
+ * walk_test / walk_batch, (c) the four device-side "walker" classes and (d)
+ * the command-line flags.  Each declaration below names the part of the
+ * reference it stands in for (path:line inside the reference project).
+ */
+#ifndef FLOWWALKER_H_
+#define FLOWWALKER_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FW_OK 0
+#define FW_ERR_ARG (-1)     /* bad argument */
+#define FW_ERR_IO (-2)      /* missing / truncated / inconsistent file */
+#define FW_ERR_CUDA (-3)    /* a CUDA runtime call failed */
+#define FW_ERR_NOMEM (-4)   /* host or device allocation failed */
+#define FW_ERR_DEVICE (-5)  /* the kernel reported an error status */
+
+/* Applications: include/app.cuh:58-152 (Deepwalk, PPR, Node2vec, Metapath). */
+#define FW_APP_DEEPWALK 0
+#define FW_APP_PPR 1
+#define FW_APP_NODE2VEC 2
+#define FW_APP_METAPATH 3
+
+/* Sampler granularity: how many neighbours share one exponential key. */
+#define FW_GROUP_EDGE 1    /* one key per neighbour */
+#define FW_GROUP_STRIP 16  /* one key per strip of up to 16 neighbours (default) */
+
+/* Bits of fw_walk_stats.device_status (0 = clean run). */
+#define FW_STATUS_BAD_START 1u     /* a start vertex outside [0,V) (walk has 0 steps) */
+#define FW_STATUS_BAD_NEIGHBOR 2u  /* a neighbour id outside [0,V) (walk ended there) */
+#define FW_STATUS_WAIT_TIMEOUT 4u  /* a bounded wait on a staged copy ran out */
+
+typedef struct fw_graph fw_graph;   /* host CSR: include/graph.cuh:44-51 */
+typedef struct fw_engine fw_engine; /* device CSR replica on one GPU: include/gpu_graph.cuh:28-78 */
+
+/*
+ * Walk parameters.  Stands in for the constructor arguments of the walker
+ * classes (include/app.cuh:47-50, 78-82, 102-107, 135-140) and the flags that
+ * feed them (src/main.cu:43, 54-58).  `d` is the number of steps (--d); the
+ * result has d+1 columns, which is what the reference calls max_depth.
+ */
+typedef struct fw_walk_params {
+  int32_t app;            /* FW_APP_* */
+  int32_t d;              /* steps per walk; MetaPath callers pass the schema length */
+  double tp;              /* PPR: stop probability after every step (--tp) */
+  double p;               /* node2vec return parameter (--p) */
+  double q;               /* node2vec in-out parameter (--q) */
+  const int32_t* schema;  /* MetaPath: edge label wanted at step k is schema[k % schema_len] */
+  int32_t schema_len;
+  int32_t group_mode;     /* FW_GROUP_*; 0 selects the default */
+  uint64_t seed;          /* Philox key; the reference hard-codes 1337 (include/walker.cuh:1324) */
+  uint64_t query_id_base; /* global id of starts[0]; walk i is keyed by query_id_base + i */
+} fw_walk_params;
+
+typedef struct fw_walk_stats {
+  uint64_t steps;         /* result cells != -1 beyond column 0 (src/main.cu:103) */
+  uint64_t scanned;       /* sum of out-degrees stepped from (src/main.cu:104-105) */
+  double device_ms;       /* CUDA-event time of the walk kernel(s) only */
+  double total_ms;        /* fw_walk only: copies + kernel, event-timed on the engine's stream */
+  uint32_t device_status; /* FW_STATUS_* bits */
+  uint32_t launches;      /* kernel launches issued by this call */
+} fw_walk_stats;
+
+/* R-MAT generator parameters (stand-in for the datasets of data/get_dataset.sh). */
+typedef struct fw_rmat_params {
+  int32_t scale;          /* ids have `scale` bits */
+  int32_t xadj_bits;      /* 32 or 64 */
+  int64_t draws;          /* candidate edges drawn (scale-22 edge factor 16: 16 << 22) */
+  double a, b, c;         /* quadrant probabilities (d = 1-a-b-c) */
+  uint64_t seed;          /* graph seed */
+  int64_t v_limit;        /* > 0: vertex count; candidates touching ids >= v_limit are dropped */
+  int64_t e_target;       /* > 0: keep drawing (beyond `draws`) until exactly this many distinct edges */
+  float weight_lo, weight_hi; /* weights uniform in [lo, hi); lo == hi == 0 -> no weights */
+  uint64_t weight_seed;
+  int32_t n_labels;       /* labels uniform in {0..n_labels-1}; 0 -> no labels */
+  uint64_t label_seed;
+  int32_t device;         /* >= 0: generate on that GPU; -1: on the host */
+} fw_rmat_params;
+
+const char* fw_last_error(void);
+
+/* ---- graph: on-disk format of include/graph.cuh:93-190, writer data/EdgeListToCSR.cpp:217-251 ---- */
+
+/* Reads <prefix>_xadj.bin, _edge.bin and, as asked, _weight.bin / _label.bin.
+ * The reference reads weights xor labels depending on --metapath
+ * (include/graph.cuh:145-185).  A 64-bit offset file (8-byte header followed
+ * by int64 offsets) is recognised by its size. */
+int fw_graph_load(const char* prefix, int need_weight, int need_label, fw_graph** out);
+int fw_graph_save(const fw_graph* g, const char* prefix);
+/* Copies the arrays.  xadj_bits: 32 (uint32) or 64 (int64). weight / label may be NULL. */
+int fw_graph_from_arrays(int64_t V, int64_t E, const void* xadj, int xadj_bits,
+                         const int32_t* adj, const float* weight,
+                         const int32_t* label, fw_graph** out);
+int fw_rmat_generate(const fw_rmat_params* params, fw_graph** out);
+int fw_graph_info(const fw_graph* g, int64_t* V, int64_t* E, int32_t* xadj_bits,
+                  int32_t* has_weight, int32_t* has_label);
+/* Borrowed pointers into the graph (valid until fw_graph_destroy). */
+int fw_graph_arrays(const fw_graph* g, const void** xadj, const int32_t** adj,
+                    const float** weight, const int32_t** label);
+/* Index of the vertex of largest out-degree (include/graph.cuh get_maxdegree_offset,
+ * used for the PPR start points in src/main.cu:277-281). */
+int fw_graph_max_degree(const fw_graph* g, int64_t* vertex, int64_t* degree);
+void fw_graph_destroy(fw_graph* g);
+
+/* ---- engine: gpu_graph construction (include/gpu_graph.cuh:39-78) ---- */
+
+/* Uploads (replicates) the graph to `device`.  which: bit 0 = weights, bit 1 = labels;
+ * 0 uploads whatever the graph has. */
+int fw_engine_create(const fw_graph* g, int device, int which, fw_engine** out);
+void fw_engine_destroy(fw_engine* e);
+int fw_engine_device(const fw_engine* e, int* device, int* sm_count);
+
+/*
+ * walk_test (include/walker.cuh:49-52, src/walk.cu:527-574): start points on
+ * the host, result left on the device.  Here the caller owns both device
+ * buffers: starts_dev int32[n], result_dev int32[n*(d+1)] (fully written,
+ * -1 padded; no memset needed).  `stream` is a cudaStream_t (NULL = the
+ * engine's own stream).  Returns after the kernel has finished.  len_hist
+ * (optional, host) receives d+1 walk-length counts.
+ */
+int fw_walk_device(fw_engine* e, const fw_walk_params* params,
+                   const int32_t* starts_dev, int64_t n, int32_t* result_dev,
+                   void* stream, fw_walk_stats* stats, uint64_t* len_hist);
+
+/*
+ * Host-buffer form of the same call: copies starts_host to the device, walks,
+ * copies the result back into result_host (int32[n*(d+1)]).  total_ms covers
+ * both copies and the kernel.
+ */
+int fw_walk(fw_engine* e, const fw_walk_params* params, const int32_t* starts_host,
+            int64_t n, int32_t* result_host, fw_walk_stats* stats, uint64_t* len_hist);
+
+/*
+ * walk_batch (include/walker.cuh:54-57, src/walk.cu:373-466, 576-649): walks
+ * n queries in batches of batch_size on two streams, double-buffered, each
+ * batch's result copied to pinned host memory while the next one runs.
+ * *result_pinned is allocated by the callee with cudaMallocHost as in the
+ * reference (src/walk.cu:586); release it with fw_free_pinned.  batch_size <= 0
+ * picks a size from free device memory minus headroom_mb, as --autobatch does
+ * (src/main.cu:259-271).
+ */
+int fw_walk_batch(fw_engine* e, const fw_walk_params* params, const int32_t* starts_host,
+                  int64_t n, int64_t batch_size, int32_t headroom_mb,
+                  int32_t** result_pinned, fw_walk_stats* stats, uint64_t* len_hist);
+void fw_free_pinned(void* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLOWWALKER_H_ */

@@ -1,0 +1,111 @@
+"""Bit-exact parity of the CUDA engine (through the C ABI) with the CPU golden walker."""
+import numpy as np
+import pytest
+
+import flowwalker_artifact_b200 as fw
+import graphs
+import oracle_lib as O
+
+pytestmark = pytest.mark.gpu
+
+APPS = [
+    (fw.APP_DEEPWALK, dict(d=80)),
+    (fw.APP_PPR, dict(d=80, tp=0.2)),
+    (fw.APP_NODE2VEC, dict(d=80, p=2.0, q=0.5)),
+    (fw.APP_METAPATH, dict(d=5, schema=[0, 1, 2, 3, 4])),
+]
+MODES = [fw.GROUP_STRIP, fw.GROUP_EDGE]
+
+
+def run_both(arrs, app, kw, starts, mode, seed=1337, base=0):
+    g = fw.Graph.from_arrays(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"])
+    eng = fw.Engine(g, 0)
+    prm = fw.make_params(app, group_mode=mode, seed=seed, query_id_base=base, **kw)
+    res, st, hist = eng.walk(prm, starts, want_hist=True)
+    ref, steps, scanned, rhist = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], app,
+                                        starts, seed=seed, query_id_base=base, group_mode=mode, **kw)
+    eng.close()
+    g.close()
+    return res, st, hist, ref, steps, scanned, rhist
+
+
+def assert_same(out):
+    res, st, hist, ref, steps, scanned, rhist = out
+    bad = np.nonzero((res != ref).any(axis=1))[0]
+    assert len(bad) == 0, "walks differ, first at query %d:\n%s\n%s" % (bad[0], res[bad[0]], ref[bad[0]])
+    assert st.steps == steps and st.scanned == scanned
+    assert (hist == rhist).all()
+    assert st.device_status == 0
+    assert st.launches == 1
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("app,kw", APPS)
+def test_config1(app, kw, mode):
+    g = graphs.config1()
+    arrs = dict(xadj=g.xadj.copy(), adj=g.adj.copy(), weight=g.weight.copy(), label=g.label.copy())
+    assert_same(run_both(arrs, app, kw, graphs.config1_starts(), mode))
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("app,kw", APPS)
+def test_ragged_rows(app, kw, mode, bits):
+    arrs = graphs.ragged(np.uint32 if bits == 32 else np.int64)
+    starts = np.concatenate([np.arange(arrs["n_rows"]), np.arange(arrs["n_rows"])]).astype(np.int32)
+    kw = dict(kw)
+    kw["d"] = min(kw["d"], 12)
+    assert_same(run_both(arrs, app, kw, starts, mode, seed=99, base=1 << 33))
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("app,kw", APPS[:3])
+def test_star_hub(app, kw, mode):
+    arrs = graphs.star()
+    starts = np.zeros(64, dtype=np.int32)
+    kw = dict(kw)
+    kw["d"] = 10
+    assert_same(run_both(arrs, app, kw, starts, mode))
+
+
+@pytest.mark.parametrize("app,kw", APPS)
+def test_rmat16_many_queries(app, kw):
+    g = fw.rmat(16, 16 << 16, weight_range=(0.0, 1.0), n_labels=5)
+    arrs = dict(xadj=g.xadj.copy(), adj=g.adj.copy(), weight=g.weight.copy(), label=g.label.copy())
+    starts = np.arange(g.V, dtype=np.int32)
+    kw = dict(kw)
+    kw["d"] = min(kw["d"], 20)
+    assert_same(run_both(arrs, app, kw, starts, fw.GROUP_STRIP))
+
+
+def test_empty_and_bad_inputs():
+    arrs = graphs.ragged()
+    g = fw.Graph.from_arrays(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"])
+    eng = fw.Engine(g, 0)
+    prm = fw.make_params(fw.APP_DEEPWALK, d=4)
+    res, st = eng.walk(prm, np.zeros(0, dtype=np.int32))
+    assert res.shape == (0, 5) and st.steps == 0 and st.launches == 0
+    res, st = eng.walk(prm, np.array([-5, 10 ** 6, 3], dtype=np.int32))
+    assert st.device_status & 1
+    assert (res[0, 1:] == -1).all() and res[0, 0] == -5 and (res[1, 1:] == -1).all()
+    res0, st0 = eng.walk(fw.make_params(fw.APP_DEEPWALK, d=0), np.array([3, 4], dtype=np.int32))
+    assert res0.tolist() == [[3], [4]] and st0.steps == 0
+    with pytest.raises(fw.FlowWalkerError):
+        eng.walk(fw.make_params(fw.APP_METAPATH, d=5), np.array([1], dtype=np.int32))  # no schema
+    with pytest.raises(fw.FlowWalkerError):
+        eng.walk(fw.make_params(7, d=5), np.array([1], dtype=np.int32))
+    eng.close()
+
+
+def test_shards_union_equals_single_run():
+    """Query ids key the random stream: two shards with their id bases reproduce the 1-GPU run."""
+    g = graphs.config1()
+    eng = fw.Engine(g, 0)
+    starts = graphs.config1_starts(1000)
+    full, _ = eng.walk(fw.make_params(fw.APP_DEEPWALK, d=40), starts)
+    a, _ = eng.walk(fw.make_params(fw.APP_DEEPWALK, d=40, query_id_base=0), starts[:500])
+    b, _ = eng.walk(fw.make_params(fw.APP_DEEPWALK, d=40, query_id_base=500), starts[500:])
+    assert (np.vstack([a, b]) == full).all()
+    out, st = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=128)
+    assert (out == full).all() and st.launches == 8
+    eng.close()
