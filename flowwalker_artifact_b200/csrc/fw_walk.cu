@@ -647,3 +647,121 @@ extern "C" int fw_walk_batch(fw_engine* e, const fw_walk_params* p, const int32_
   *result_pinned = pinned;
   return FW_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free entry point
+// ---------------------------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory at call time: a
+// plugin running inside another framework's memory pool that has already
+// reserved the whole GPU, a latency-critical serving loop where a cudaMalloc
+// would serialise the device, or code running after start-up in a process
+// whose allocator has been frozen.  For them the walk's scratch (the query
+// counter, the step/scanned/status counters and the walk-length histogram)
+// lives in a fixed array that is part of the loaded module.  Every GPU that
+// loads the library holds these 32 KB + 32 B until the process exits.
+namespace {
+constexpr int kNoAllocMaxD = 4095;  // largest `d` the fixed scratch can serve
+constexpr int kNoAllocWords = kSlotHist + kNoAllocMaxD + 1;
+constexpr int kNoAllocMaxDevices = 64;
+}  // namespace
+
+static __device__ __align__(256) unsigned long long g_noalloc_scratch[kNoAllocWords];
+
+namespace {
+// Device address of g_noalloc_scratch per device ordinal.  In host code the
+// array's name is only a handle for the runtime, so the address each kernel
+// receives is looked up once per device, with that device current.
+unsigned long long* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+int noalloc_scratch_for(int device, unsigned long long** out) {
+  if (device < 0 || device >= kNoAllocMaxDevices)
+    return fw::fail(FW_ERR_ARG, "device ordinal %d is beyond the %d this entry point supports", device,
+                    kNoAllocMaxDevices);
+  if (!g_noalloc_ptr[device]) {
+    void* p = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (err != cudaSuccess || !p)
+      return fw::fail(FW_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", device,
+                      cudaGetErrorString(err));
+    g_noalloc_ptr[device] = static_cast<unsigned long long*>(p);
+  }
+  *out = g_noalloc_ptr[device];
+  return FW_OK;
+}
+}  // namespace
+
+extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void* xadj_dev, int xadj_bits,
+                                   const int32_t* adj_dev, const float* weight_dev,
+                                   const int32_t* label_dev, const fw_walk_params* p,
+                                   const int32_t* starts_dev, int64_t n, int32_t* result_dev,
+                                   void* stream, fw_walk_stats* stats, uint64_t* len_hist) {
+  fw::clear_error();
+  if (!p) return fw::fail(FW_ERR_ARG, "null params");
+  if (V < 0 || E < 0 || n < 0 || !xadj_dev || !adj_dev) return fw::fail(FW_ERR_ARG, "bad sizes or null CSR arrays");
+  if (xadj_bits != 32 && xadj_bits != 64) return fw::fail(FW_ERR_ARG, "xadj_bits must be 32 or 64");
+  if (p->app < FW_APP_DEEPWALK || p->app > FW_APP_METAPATH) return fw::fail(FW_ERR_ARG, "unknown app %d", p->app);
+  if (p->d < 0 || p->d > kNoAllocMaxD)
+    return fw::fail(FW_ERR_ARG, "d=%d exceeds the fixed scratch of this entry point (max %d); use fw_walk_device",
+                    p->d, kNoAllocMaxD);
+  if (p->group_mode != 0 && p->group_mode != FW_GROUP_EDGE && p->group_mode != FW_GROUP_STRIP)
+    return fw::fail(FW_ERR_ARG, "group_mode must be 0, %d or %d", FW_GROUP_EDGE, FW_GROUP_STRIP);
+  if (p->app == FW_APP_METAPATH) {
+    if (!label_dev) return fw::fail(FW_ERR_ARG, "MetaPath needs edge labels");
+    if (!p->schema || p->schema_len <= 0 || p->schema_len > kMaxSchema)
+      return fw::fail(FW_ERR_ARG, "schema length must be in 1..%d", kMaxSchema);
+  } else if (!weight_dev) {
+    return fw::fail(FW_ERR_ARG, "this app needs edge weights");
+  }
+  if (p->app == FW_APP_NODE2VEC && !(p->p > 0.0 && p->q > 0.0)) return fw::fail(FW_ERR_ARG, "node2vec needs p > 0 and q > 0");
+  if (n > 0 && (!starts_dev || !result_dev)) return fw::fail(FW_ERR_ARG, "null device buffer");
+  if (((uintptr_t)adj_dev | (uintptr_t)weight_dev | (uintptr_t)label_dev) & 15u)
+    return fw::fail(FW_ERR_ARG, "edge arrays must be 16-byte aligned");
+  DeviceGuard guard(device);
+  unsigned long long* scratch = nullptr;
+  int rc = noalloc_scratch_for(device, &scratch);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  WalkArgs a;
+  a.xadj = xadj_dev; a.adj = adj_dev; a.weight = weight_dev; a.label = label_dev;
+  a.V = V; a.starts = starts_dev; a.n = n; a.result = result_dev; a.scratch = scratch;
+  a.qid_base = p->query_id_base; a.d = p->d;
+  a.tp_thresh = fw::tp_threshold(p->tp);
+  a.inv_p = (float)(1.0 / p->p); a.inv_q = (float)(1.0 / p->q);
+  a.k0 = (uint32_t)p->seed; a.k1 = (uint32_t)(p->seed >> 32);
+  a.hist_in_smem = 1;  // d + 1 <= 4096 words always fits
+  a.schema_len = p->app == FW_APP_METAPATH ? p->schema_len : 1;
+  for (int i = 0; i < kMaxSchema; ++i)
+    a.schema[i] = (p->app == FW_APP_METAPATH && i < p->schema_len) ? p->schema[i] : 0;
+  KernelFn fn = pick_kernel(p->app, p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode, xadj_bits);
+  const size_t smem = (size_t)(p->d + 1) * 4;
+  int per_sm = 0, sms = 0;
+  FW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
+  FW_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  if (per_sm < 1) return fw::fail(FW_ERR_CUDA, "walk kernel does not fit on an SM");
+  const size_t words = (size_t)kSlotHist + (size_t)p->d + 1;
+  // the array keeps the previous call's counters: everything this call reads starts at zero
+  FW_CUDA(cudaMemsetAsync(scratch, 0, words * 8, st));
+  if (n > 0) {
+    const int64_t want = (n + (kThreads / 32) * kClaim - 1) / ((kThreads / 32) * kClaim);
+    const int grid = (int)std::min<int64_t>((int64_t)sms * per_sm, std::max<int64_t>(want, 1));
+    void* params[] = {&a};
+    FW_CUDA(cudaLaunchKernel((const void*)fn, dim3(grid), dim3(kThreads), params, smem, st));
+  }
+  // counters go straight into the caller's memory, in two plain copies
+  unsigned long long head[kSlotHist];
+  FW_CUDA(cudaMemcpyAsync(head, scratch, sizeof(head), cudaMemcpyDeviceToHost, st));
+  if (len_hist)
+    FW_CUDA(cudaMemcpyAsync(len_hist, scratch + kSlotHist, (size_t)(p->d + 1) * 8, cudaMemcpyDeviceToHost, st));
+  FW_CUDA(cudaStreamSynchronize(st));
+  if (stats) {
+    stats->steps = head[kSlotSteps];
+    stats->scanned = head[kSlotScanned];
+    stats->device_status = (uint32_t)head[kSlotStatus];
+    stats->device_ms = 0.0;
+    stats->total_ms = 0.0;
+    stats->launches = n > 0 ? 1 : 0;
+  }
+  return FW_OK;
+}

@@ -159,6 +159,39 @@ int fw_walk_batch(fw_engine* e, const fw_walk_params* params, const int32_t* sta
                   int32_t** result_pinned, fw_walk_stats* stats, uint64_t* len_hist);
 void fw_free_pinned(void* p);
 
+/*
+ * Allocation-free walk.  No counterpart in the reference (its host code
+ * allocates at every call, src/walk.cu:98-138, 586).
+ *
+ * For callers that cannot allocate device memory when they call: a plugin
+ * living inside another framework's memory pool that already owns the GPU, a
+ * serving loop that must not hit the device-wide synchronisation of
+ * cudaMalloc/cudaFree, a process whose allocator is frozen after start-up.
+ * The caller passes the CSR, the start points and the result as device
+ * pointers on `device`; the walk's scratch (query counter, counters,
+ * walk-length histogram) is a fixed 32 KB array inside the loaded module, so
+ * this call performs no cudaMalloc, cudaFree or other allocating call.
+ *
+ * Limits and rules:
+ *  - d <= 4095 (larger values are rejected with FW_ERR_ARG: use fw_walk_device);
+ *    device ordinal < 64; schema_len <= 64.
+ *  - adj_dev / weight_dev / label_dev must be 16-byte aligned and readable up
+ *    to the next multiple of 4 elements past E (the kernel reads whole
+ *    16-byte quads); weight_dev may be NULL for MetaPath, label_dev otherwise.
+ *  - The first call on each device looks up the scratch address
+ *    (cudaGetSymbolAddress); make that first call before any stream capture.
+ *  - All calls on one device share the scratch array, which keeps the last
+ *    call's contents; each call clears what it uses, so calls must not overlap
+ *    on the GPU (two streams, or two host threads on the same device, race).
+ *  - Returns after the kernel has finished; stats->device_ms / total_ms are
+ *    not measured (0) since events would have to be created.  len_hist
+ *    (optional, host, d+1 words) receives the walk-length counts.
+ */
+int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void* xadj_dev, int xadj_bits,
+                        const int32_t* adj_dev, const float* weight_dev, const int32_t* label_dev,
+                        const fw_walk_params* params, const int32_t* starts_dev, int64_t n,
+                        int32_t* result_dev, void* stream, fw_walk_stats* stats, uint64_t* len_hist);
+
 #ifdef __cplusplus
 }
 #endif
