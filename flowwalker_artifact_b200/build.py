@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libflowwalker.so")
 CLI = os.path.join(HERE, "flowwalker")
 SOURCES = ["fw_graph.cpp", "fw_rmat.cu", "fw_walk.cu"]
-HEADERS = ["fw_internal.h", "fw_spec.cuh", os.path.join("..", "..", "include", "flowwalker.h")]
+HEADERS = ["fw_internal.h", "fw_spec.cuh", "fw_kernels.cuh", os.path.join("..", "..", "include", "flowwalker.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     # no implicit a*b+c contraction: the walk must match the CPU golden walker bit for bit

@@ -1,0 +1,500 @@
+// Device code of the walk engine (sm_100a).
+//
+// One persistent grid; every warp claims queries from a global atomic counter
+// and walks them to completion.  Per step the row of the current vertex is
+// swept in 2 KB supergroups with aligned 128-bit accesses:
+//   * short rows: straight from global memory (four independent loads per lane);
+//   * long rows : through a per-warp ring in shared memory filled by TMA bulk
+//                 copies (cp.async.bulk + mbarrier), so the next supergroups are
+//                 in flight while the current one is reduced.
+// Stands in for include/walker.cuh:1307-1580, include/sampler.cuh:46-200,
+// include/app.cuh:58-152, include/gpu_task.cuh:24-78 and include/myrand.cuh
+// of the reference.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/flowwalker.h"
+#include "fw_spec.cuh"
+
+namespace fwk {
+
+constexpr int kMaxSchema = 64;
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreads = 32 * kWarpsPerCta;
+constexpr int kClaim = 4;                // queries claimed per atomic
+constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared memory up to this d+1
+constexpr int kStages = 2;               // ring depth per warp
+constexpr uint32_t kSuperBytes = 16u * fw::kQuadsPerSuper;  // 2 KB
+constexpr uint32_t kRingMinSuper = 3;    // rows with at least this many supergroups use the ring
+constexpr uint32_t kWaitLimit = 1u << 22;  // polls of an mbarrier before giving up
+
+// Scratch words (uint64) in device memory.
+constexpr int kSlotSteps = 0, kSlotScanned = 1, kSlotStatus = 2, kSlotCounter = 3, kSlotHist = 4;
+
+struct WalkArgs {
+  const void* xadj;
+  const int32_t* adj;
+  const float* weight;
+  const int32_t* label;
+  int64_t V;
+  const int32_t* starts;
+  int64_t n;
+  int32_t* result;
+  unsigned long long* scratch;
+  uint64_t qid_base;
+  int32_t d;
+  uint32_t tp_thresh;
+  float inv_p, inv_q;
+  uint32_t k0, k1;
+  int32_t hist_in_smem;
+  int32_t schema_len;
+  int32_t schema[kMaxSchema];
+};
+
+// Per-step context.
+struct StepCtx {
+  const int4* prim;  // weight (or label) quads of the row: quad q is prim[q]
+  const int4* sec;   // neighbour-id quads of the row (node2vec)
+  uint32_t nq;       // quads in the row
+  uint32_t head;     // first valid edge, relative to quad 0
+  uint32_t tail;     // one past the last valid edge, relative to quad 0
+  int32_t prev;      // previous vertex or -1
+  int64_t pb, pe;    // row of prev (node2vec)
+  int32_t want;      // label wanted (MetaPath)
+};
+
+// ---- PTX wrappers: mbarrier + bulk async copy (TMA, no multicast) ----
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// global -> this CTA's shared memory; both addresses 16-byte aligned, bytes % 16 == 0
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// Bounded wait: false when the copy did not land within kWaitLimit polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// ---- bias of one quad ----
+
+__device__ __forceinline__ float pos(float x) { return fmaxf(x, 0.0f); }
+
+// include/gpu_graph.cuh:97-118: membership of `target` in a sorted row.
+__device__ __forceinline__ bool row_contains(const int32_t* __restrict__ adj, int64_t lo, int64_t hi,
+                                             int32_t target) {
+  --hi;
+  while (lo <= hi) {
+    const int64_t mid = lo + ((hi - lo) >> 1);
+    const int32_t a = __ldg(adj + mid);
+    if (a == target) return true;
+    if (a < target) lo = mid + 1; else hi = mid - 1;
+  }
+  return false;
+}
+
+// Biases of the four edges of quad q from its raw 16 bytes (`nb`: the four
+// neighbour ids, node2vec only).  `edges`: the quad may be the first or last of
+// the row, whose edges outside [head, tail) get bias 0.  CLEAN: the weights are
+// known to be >= 0 and not NaN, so the clamp is skipped.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c, int4 raw, int4 nb,
+                                            uint32_t q, bool edges) {
+  float4 v;
+  if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
+    v.x = raw.x == c.want ? 1.0f : 0.0f;
+    v.y = raw.y == c.want ? 1.0f : 0.0f;
+    v.z = raw.z == c.want ? 1.0f : 0.0f;
+    v.w = raw.w == c.want ? 1.0f : 0.0f;
+  } else {
+    v = make_float4(__int_as_float(raw.x), __int_as_float(raw.y), __int_as_float(raw.z), __int_as_float(raw.w));
+    if (APP == FW_APP_NODE2VEC && c.prev >= 0) {  // include/app.cuh:109-122
+      const int32_t xs[4] = {nb.x, nb.y, nb.z, nb.w};
+      float vs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t r = 4u * q + k;
+        if (r < c.head || r >= c.tail) continue;
+        if (xs[k] == c.prev) vs[k] = __fmul_rn(vs[k], a.inv_p);
+        else if (!row_contains(a.adj, c.pb, c.pe, xs[k])) vs[k] = __fmul_rn(vs[k], a.inv_q);
+      }
+      v = make_float4(vs[0], vs[1], vs[2], vs[3]);
+    }
+    if (!CLEAN) { v.x = pos(v.x); v.y = pos(v.y); v.z = pos(v.z); v.w = pos(v.w); }
+  }
+  if (edges && (q == 0 || q + 1 == c.nq)) {
+    const uint32_t r = 4u * q;
+    if (r + 0 < c.head || r + 0 >= c.tail) v.x = 0.0f;
+    if (r + 1 < c.head || r + 1 >= c.tail) v.y = 0.0f;
+    if (r + 2 < c.head || r + 2 >= c.tail) v.z = 0.0f;
+    if (r + 3 < c.head || r + 3 >= c.tail) v.w = 0.0f;
+  }
+  return v;
+}
+
+__device__ __forceinline__ float sum4(const float4 v) {
+  return __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w));
+}
+__device__ __forceinline__ float sum_strip(const float S[4]) {
+  return __fadd_rn(__fadd_rn(S[0], S[1]), __fadd_rn(S[2], S[3]));
+}
+
+// Total bias of lane `lane`'s strip of supergroup s, read from global memory.
+// `interior`: all 128 quads exist and none is a boundary quad.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ float strip_weight_global(const WalkArgs& a, const StepCtx& c, uint32_t s,
+                                                     int lane, bool interior, float4* keep) {
+  const uint32_t base = s * fw::kQuadsPerSuper + lane;
+  const int4 zero = make_int4(0, 0, 0, 0);
+  float S[4];
+  if (interior) {
+    int4 raw[4], nb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) raw[j] = __ldg(c.prim + base + 32u * j);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? __ldg(c.sec + base + 32u * j) : zero;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 v = quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], base + 32u * j, false);
+      if (keep) keep[j] = v;
+      S[j] = sum4(v);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t q = base + 32u * j;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s * fw::kQuadsPerSuper + 32u * j < c.nq) {  // warp-uniform: skip empty quarter sweeps
+        if (q < c.nq) {
+          const int4 raw = __ldg(c.prim + q);
+          const int4 nb = APP == FW_APP_NODE2VEC ? __ldg(c.sec + q) : zero;
+          v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, true);
+        }
+      }
+      if (keep) keep[j] = v;
+      S[j] = sum4(v);
+    }
+  }
+  return sum_strip(S);
+}
+
+// Same from a staged supergroup in shared memory (interior supergroups only).
+template <int APP, bool CLEAN>
+__device__ __forceinline__ float strip_weight_staged(const WalkArgs& a, const StepCtx& c, uint32_t s, int lane,
+                                                     const int4* st_prim, const int4* st_sec) {
+  const uint32_t base = s * fw::kQuadsPerSuper + lane;
+  const int4 zero = make_int4(0, 0, 0, 0);
+  int4 raw[4], nb[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) raw[j] = st_prim[lane + 32 * j];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? st_sec[lane + 32 * j] : zero;
+  float S[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) S[j] = sum4(quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], base + 32u * j, false));
+  return sum_strip(S);
+}
+
+// Smallest (key, id) over the warp; ids are unique.
+__device__ __forceinline__ void warp_argmin(uint32_t& key, uint32_t& id) {
+  const uint32_t m = __reduce_min_sync(0xFFFFFFFFu, key);
+  id = __reduce_min_sync(0xFFFFFFFFu, key == m ? id : 0xFFFFFFFFu);
+  key = m;
+}
+
+__device__ __forceinline__ uint32_t word_of(const fw::Philox4& r, uint32_t k) {
+  return k == 0 ? r.x : k == 1 ? r.y : k == 2 ? r.z : r.w;
+}
+
+// Per-warp ring state.
+struct Ring {
+  uint32_t data;    // shared address of stage 0 (stages are contiguous)
+  uint32_t bar;     // shared address of mbarrier 0 (8 bytes apart)
+  uint32_t parity;  // bit st = parity to wait for on stage st
+  bool failed;      // a wait ran out
+};
+
+template <int APP>
+__device__ __forceinline__ constexpr uint32_t stage_bytes() {
+  return APP == FW_APP_NODE2VEC ? 2u * kSuperBytes : kSuperBytes;
+}
+
+// One weighted pick in the row described by c, by one warp.  Returns the
+// edge index relative to quad 0 of the row, or 0xFFFFFFFF when no edge has
+// positive bias.
+template <int APP, int MODE, bool CLEAN>
+__device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const StepCtx& c, uint32_t step,
+                                                    uint32_t qlo, uint32_t qhi, int lane, Ring& ring,
+                                                    const unsigned char* ring_ptr) {
+  const uint32_t c1 = step | (fw::kPurposeScan << 28);
+  uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu;
+  const int4 zero = make_int4(0, 0, 0, 0);
+  if (MODE == FW_GROUP_EDGE) {
+    for (uint32_t q = lane; q < c.nq; q += 32) {
+      const int4 raw = __ldg(c.prim + q);
+      const int4 nb = APP == FW_APP_NODE2VEC ? __ldg(c.sec + q) : zero;
+      const float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, true);
+      const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.k0, a.k1);
+      const float vs[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t rs[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (vs[k] > 0.0f) {
+          const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(rs[k]), vs[k]));
+          if (bits < best_key) { best_key = bits; best_id = 4u * q + k; }
+        }
+      }
+    }
+    warp_argmin(best_key, best_id);
+    return best_id;
+  }
+
+  // ---- strips ----
+  const uint32_t nsuper = (c.nq + fw::kQuadsPerSuper - 1) / fw::kQuadsPerSuper;
+  // supergroup s is interior iff it has all its quads and holds neither quad 0 nor quad nq-1
+  auto consider = [&](uint32_t s, float W, const fw::Philox4& r) {
+    if (W > 0.0f) {
+      const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(word_of(r, s & 3u)), W));
+      if (bits < best_key) { best_key = bits; best_id = s * 32u + lane; }
+    }
+  };
+  if (nsuper < kRingMinSuper) {
+    fw::Philox4 r = fw::philox4x32_10((uint32_t)lane, c1, qlo, qhi, a.k0, a.k1);  // nsuper <= 4: one block
+    for (uint32_t s = 0; s < nsuper; ++s)
+      consider(s, strip_weight_global<APP, CLEAN>(a, c, s, lane, false, nullptr), r);
+  } else {
+    // first and last supergroups straight from global memory (boundary quads, partial fill);
+    // the interior ones through the ring
+    const uint32_t first = 1, last = nsuper - 1;  // interior = [first, last)
+    constexpr uint32_t kSB = stage_bytes<APP>();
+    if (lane == 0) {
+#pragma unroll
+      for (uint32_t t = 0; t < kStages; ++t) {
+        const uint32_t s = first + t;
+        if (s < last) {
+          const uint32_t bar = ring.bar + 8u * t;
+          mbar_expect_tx(bar, kSB);
+          bulk_g2s(ring.data + t * kSB, c.prim + (size_t)s * fw::kQuadsPerSuper, kSuperBytes, bar);
+          if (APP == FW_APP_NODE2VEC)
+            bulk_g2s(ring.data + t * kSB + kSuperBytes, c.sec + (size_t)s * fw::kQuadsPerSuper, kSuperBytes, bar);
+        }
+      }
+    }
+    fw::Philox4 r = fw::philox4x32_10((uint32_t)lane, c1, qlo, qhi, a.k0, a.k1);
+    consider(0, strip_weight_global<APP, CLEAN>(a, c, 0, lane, false, nullptr), r);
+    uint32_t t = 0;
+    for (uint32_t s = first; s < last; ++s) {
+      if ((s & 3u) == 0) r = fw::philox4x32_10((s >> 2) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+      const uint32_t bar = ring.bar + 8u * t;
+      float W = 0.0f;
+      if (!ring.failed) {
+        if (mbar_wait(bar, (ring.parity >> t) & 1u)) {
+          ring.parity ^= 1u << t;
+          const int4* st = reinterpret_cast<const int4*>(ring_ptr + t * kSB);
+          W = strip_weight_staged<APP, CLEAN>(a, c, s, lane, st, st + fw::kQuadsPerSuper);
+        } else {
+          ring.failed = true;
+        }
+      }
+      consider(s, W, r);  // consumes the staged values before the stage is handed back
+      ring.failed = __any_sync(0xFFFFFFFFu, ring.failed);
+      // every lane has consumed the stage: refill it with supergroup s + kStages
+      if (lane == 0 && !ring.failed && s + kStages < last) {
+        mbar_expect_tx(bar, kSB);
+        bulk_g2s(ring.data + t * kSB, c.prim + (size_t)(s + kStages) * fw::kQuadsPerSuper, kSuperBytes, bar);
+        if (APP == FW_APP_NODE2VEC)
+          bulk_g2s(ring.data + t * kSB + kSuperBytes, c.sec + (size_t)(s + kStages) * fw::kQuadsPerSuper,
+                   kSuperBytes, bar);
+      }
+      t = t + 1 == kStages ? 0 : t + 1;
+    }
+    if ((last & 3u) == 0) r = fw::philox4x32_10((last >> 2) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+    consider(last, strip_weight_global<APP, CLEAN>(a, c, last, lane, false, nullptr), r);
+    if (ring.failed) return 0xFFFFFFFFu;
+  }
+  warp_argmin(best_key, best_id);
+  if (best_id == 0xFFFFFFFFu) return best_id;
+  // inverse-CDF pick inside the winning strip (every lane computes the same)
+  const uint32_t B = best_id;
+  const fw::Philox4 r = fw::philox4x32_10(B, step | (fw::kPurposePick << 28), qlo, qhi, a.k0, a.k1);
+  float4 v[4];
+  const float W = strip_weight_global<APP, CLEAN>(a, c, B >> 5, (int)(B & 31u), false, v);
+  const float t = __fmul_rn((float)(r.x >> 8) * 0x1p-24f, W);
+  const uint32_t qb = (B >> 5) * fw::kQuadsPerSuper + (B & 31u);
+  float acc = 0.0f;
+  uint32_t last_pos = 0xFFFFFFFFu, chosen = 0xFFFFFFFFu;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (vs[k] > 0.0f && chosen == 0xFFFFFFFFu) {
+        last_pos = 4u * (qb + 32u * j) + k;
+        acc = __fadd_rn(acc, vs[k]);
+        if (acc > t) chosen = last_pos;
+      }
+    }
+  }
+  return chosen != 0xFFFFFFFFu ? chosen : last_pos;
+}
+
+template <int APP, int MODE, bool CLEAN, typename OffT>
+__global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_APP_NODE2VEC ? 5 : 2) walk_kernel(const __grid_constant__ WalkArgs a) {
+  extern __shared__ __align__(128) unsigned char s_dyn[];
+  __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_STRIP ? kStages * stage_bytes<APP>() : 0u;
+  uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
+  const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
+  Ring ring;
+  ring.data = smem_addr(ring_ptr);
+  ring.bar = smem_addr(&s_bar[warp][0]);
+  ring.parity = 0u;
+  ring.failed = false;
+  if (MODE == FW_GROUP_STRIP && lane == 0) {
+#pragma unroll
+    for (int t = 0; t < kStages; ++t) mbar_init(ring.bar + 8u * t, 1u);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (a.hist_in_smem)
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x) s_hist[z] = 0u;
+  __syncthreads();
+
+  const OffT* __restrict__ xadj = static_cast<const OffT*>(a.xadj);
+  const int64_t D = (int64_t)a.d + 1;
+  const int4* const prim_base = reinterpret_cast<const int4*>(APP == FW_APP_METAPATH ? (const void*)a.label
+                                                                                     : (const void*)a.weight);
+  const int4* const sec_base = reinterpret_cast<const int4*>(a.adj);
+  unsigned long long my_steps = 0, my_scanned = 0;
+  uint32_t status = 0;
+
+  while (!ring.failed) {
+    long long first = 0;
+    if (lane == 0) first = (long long)atomicAdd(a.scratch + kSlotCounter, (unsigned long long)kClaim);
+    first = __shfl_sync(0xFFFFFFFFu, first, 0);
+    if (first >= a.n) break;
+    const long long stop = first + kClaim < a.n ? first + kClaim : a.n;
+    for (long long qi = first; qi < stop && !ring.failed; ++qi) {
+      const uint64_t qid = a.qid_base + (uint64_t)qi;
+      const uint32_t qlo = (uint32_t)qid, qhi = (uint32_t)(qid >> 32);
+      int32_t* __restrict__ row_out = a.result + qi * D;
+      int32_t cur = __ldg(a.starts + qi);
+      if (lane == 0) row_out[0] = cur;
+      StepCtx c;
+      c.prev = -1; c.pb = 0; c.pe = 0; c.want = 0;
+      int k = 0;
+      if (cur < 0 || (int64_t)cur >= a.V) {
+        status |= FW_STATUS_BAD_START;
+      } else {
+        while (k < a.d) {
+          const int64_t b = (int64_t)__ldg(xadj + cur), e = (int64_t)__ldg(xadj + cur + 1);
+          if (e <= b) break;
+          const int64_t q0 = b >> 2;
+          c.prim = prim_base + q0;
+          c.sec = sec_base + q0;
+          c.nq = (uint32_t)(((e + 3) >> 2) - q0);
+          c.head = (uint32_t)(b - 4 * q0);
+          c.tail = (uint32_t)(e - 4 * q0);
+          if (APP == FW_APP_METAPATH) c.want = a.schema[k % a.schema_len];
+          const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, (uint32_t)k, qlo, qhi, lane, ring, ring_ptr);
+          if (rel == 0xFFFFFFFFu) break;  // include/walker.cuh:1373-1374 (or a failed wait)
+          const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
+          if (nxt < 0 || (int64_t)nxt >= a.V) { status |= FW_STATUS_BAD_NEIGHBOR; break; }
+          if (lane == 0) row_out[k + 1] = nxt;  // include/walker.cuh:1380-1381
+          my_scanned += (unsigned long long)(e - b);
+          c.prev = cur; c.pb = b; c.pe = e;  // include/gpu_task.cuh:70-77
+          cur = nxt;
+          ++k;
+          if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
+            const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(k - 1) | (fw::kPurposeStop << 28),
+                                                    qlo, qhi, a.k0, a.k1);
+            if (r.x < a.tp_thresh) break;
+          }
+        }
+      }
+      for (int z = k + 1 + lane; z <= a.d; z += 32) row_out[z] = -1;
+      my_steps += (unsigned long long)k;
+      if (lane == 0) {
+        if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
+        else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+      }
+    }
+  }
+  if (ring.failed) {
+    // A staged copy did not land in time.  Report it, then give the copies this
+    // warp may still have in flight one more bounded wait before its shared
+    // memory is released with the CTA.
+    status |= FW_STATUS_WAIT_TIMEOUT;
+#pragma unroll
+    for (int t = 0; t < kStages; ++t) mbar_wait(ring.bar + 8u * t, (ring.parity >> t) & 1u);
+  }
+  if (lane == 0) {
+    if (my_steps) atomicAdd(a.scratch + kSlotSteps, my_steps);
+    if (my_scanned) atomicAdd(a.scratch + kSlotScanned, my_scanned);
+    if (status) atomicOr(a.scratch + kSlotStatus, (unsigned long long)status);
+  }
+  if (a.hist_in_smem) {
+    __syncthreads();
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x)
+      if (s_hist[z]) atomicAdd(a.scratch + kSlotHist + z, (unsigned long long)s_hist[z]);
+  }
+}
+
+using KernelFn = void (*)(const WalkArgs);
+
+template <int APP, int MODE, bool CLEAN>
+inline KernelFn pick_off(int xadj_bits) {
+  return xadj_bits == 64 ? (KernelFn)walk_kernel<APP, MODE, CLEAN, int64_t>
+                         : (KernelFn)walk_kernel<APP, MODE, CLEAN, uint32_t>;
+}
+template <int APP>
+inline KernelFn pick_mode(int mode, bool clean, int xadj_bits) {
+  if (mode == FW_GROUP_EDGE) return pick_off<APP, FW_GROUP_EDGE, false>(xadj_bits);
+  return clean ? pick_off<APP, FW_GROUP_STRIP, true>(xadj_bits) : pick_off<APP, FW_GROUP_STRIP, false>(xadj_bits);
+}
+// clean: all weights are known to be >= 0 and not NaN
+inline KernelFn pick_kernel(int app, int mode, bool clean, int xadj_bits) {
+  switch (app) {
+    case FW_APP_DEEPWALK: return pick_mode<FW_APP_DEEPWALK>(mode, clean, xadj_bits);
+    case FW_APP_PPR: return pick_mode<FW_APP_PPR>(mode, clean, xadj_bits);
+    case FW_APP_NODE2VEC: return pick_mode<FW_APP_NODE2VEC>(mode, clean, xadj_bits);
+    default:  // MetaPath biases are 0/1: nothing to clamp
+      return mode == FW_GROUP_EDGE ? pick_off<FW_APP_METAPATH, FW_GROUP_EDGE, false>(xadj_bits)
+                                   : pick_off<FW_APP_METAPATH, FW_GROUP_STRIP, true>(xadj_bits);
+  }
+}
+
+// Dynamic shared memory of one CTA: the warps' rings, then the histogram.
+inline size_t kernel_smem_bytes(int app, int mode, int d, bool hist_in_smem) {
+  size_t ring = 0;
+  if (mode != FW_GROUP_EDGE)
+    ring = (size_t)kWarpsPerCta * kStages * (app == FW_APP_NODE2VEC ? 2u * kSuperBytes : kSuperBytes);
+  return ring + (hist_in_smem ? (size_t)(d + 1) * 4 : 0);
+}
+
+}  // namespace fwk

@@ -20,289 +20,11 @@
 #include <new>
 
 #include "fw_internal.h"
+#include "fw_kernels.cuh"
 #include "fw_spec.cuh"
 
-namespace {
+using namespace fwk;
 
-constexpr int kMaxSchema = 64;
-constexpr int kThreads = 256;  // 8 warps per CTA
-constexpr int kClaim = 4;      // queries claimed per atomic
-constexpr int kMaxSmemHist = 8192;
-
-// Scratch words (uint64) in device memory.
-constexpr int kSlotSteps = 0, kSlotScanned = 1, kSlotStatus = 2, kSlotCounter = 3, kSlotHist = 4;
-
-struct WalkArgs {
-  const void* xadj;
-  const int32_t* adj;
-  const float* weight;
-  const int32_t* label;
-  int64_t V;
-  const int32_t* starts;
-  int64_t n;
-  int32_t* result;
-  unsigned long long* scratch;
-  uint64_t qid_base;
-  int32_t d;
-  uint32_t tp_thresh;
-  float inv_p, inv_q;
-  uint32_t k0, k1;
-  int32_t hist_in_smem;
-  int32_t schema_len;
-  int32_t schema[kMaxSchema];
-};
-
-struct Row {
-  int64_t b, e;  // absolute edge range
-};
-
-// Per-step context handed to the bias loaders.
-struct StepCtx {
-  int64_t q0;     // b >> 2
-  uint32_t nq;    // quads in the row
-  uint32_t head;  // b - 4*q0
-  uint32_t tail;  // e - 4*q0
-  int32_t prev;   // previous vertex or -1
-  int64_t pb, pe; // row of prev (node2vec)
-  int32_t want;   // label wanted (MetaPath)
-};
-
-__device__ __forceinline__ float pos(float x) { return fmaxf(x, 0.0f); }
-
-// include/gpu_graph.cuh:97-118: membership of `target` in a sorted row.
-__device__ __forceinline__ bool row_contains(const int32_t* __restrict__ adj, int64_t lo, int64_t hi,
-                                             int32_t target) {
-  --hi;
-  while (lo <= hi) {
-    const int64_t mid = lo + ((hi - lo) >> 1);
-    const int32_t a = __ldg(adj + mid);
-    if (a == target) return true;
-    if (a < target) lo = mid + 1; else hi = mid - 1;
-  }
-  return false;
-}
-
-// Biases of the four edges of quad q (0 for edges outside the row and for
-// non-positive or NaN biases).
-template <int APP>
-__device__ __forceinline__ float4 load_bias4(const WalkArgs& a, const StepCtx& c, uint32_t q) {
-  float4 v;
-  if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
-    const int4 l = __ldg(reinterpret_cast<const int4*>(a.label) + (c.q0 + q));
-    v.x = l.x == c.want ? 1.0f : 0.0f;
-    v.y = l.y == c.want ? 1.0f : 0.0f;
-    v.z = l.z == c.want ? 1.0f : 0.0f;
-    v.w = l.w == c.want ? 1.0f : 0.0f;
-  } else {
-    v = __ldg(reinterpret_cast<const float4*>(a.weight) + (c.q0 + q));
-    if (APP == FW_APP_NODE2VEC && c.prev >= 0) {  // include/app.cuh:109-122
-      const int4 x = __ldg(reinterpret_cast<const int4*>(a.adj) + (c.q0 + q));
-      const int32_t xs[4] = {x.x, x.y, x.z, x.w};
-      float* vs = &v.x;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t r = 4u * q + k;
-        if (r < c.head || r >= c.tail) continue;
-        if (xs[k] == c.prev) vs[k] = __fmul_rn(vs[k], a.inv_p);
-        else if (!row_contains(a.adj, c.pb, c.pe, xs[k])) vs[k] = __fmul_rn(vs[k], a.inv_q);
-      }
-    }
-    v.x = pos(v.x); v.y = pos(v.y); v.z = pos(v.z); v.w = pos(v.w);
-  }
-  if (q == 0 || q + 1 == c.nq) {
-    const uint32_t r = 4u * q;
-    if (r + 0 < c.head || r + 0 >= c.tail) v.x = 0.0f;
-    if (r + 1 < c.head || r + 1 >= c.tail) v.y = 0.0f;
-    if (r + 2 < c.head || r + 2 >= c.tail) v.z = 0.0f;
-    if (r + 3 < c.head || r + 3 >= c.tail) v.w = 0.0f;
-  }
-  return v;
-}
-
-__device__ __forceinline__ float sum4(const float4 v) {
-  return __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w));
-}
-
-// Smallest (key, id) over the warp; ids are unique.
-__device__ __forceinline__ void warp_argmin(uint32_t& key, uint32_t& id) {
-  const uint32_t m = __reduce_min_sync(0xFFFFFFFFu, key);
-  id = __reduce_min_sync(0xFFFFFFFFu, key == m ? id : 0xFFFFFFFFu);
-  key = m;
-}
-
-// One weighted pick in the row described by c, by one warp.  Returns the
-// absolute edge index, or -1 when no edge has positive bias.
-template <int APP, int MODE>
-__device__ __forceinline__ int64_t sample_row_warp(const WalkArgs& a, const StepCtx& c, uint32_t c1,
-                                                   uint32_t qlo, uint32_t qhi, int lane) {
-  uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu;
-  if (MODE == FW_GROUP_EDGE) {
-    for (uint32_t q = lane; q < c.nq; q += 32) {
-      const float4 v = load_bias4<APP>(a, c, q);
-      const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.k0, a.k1);
-      const float vs[4] = {v.x, v.y, v.z, v.w};
-      const uint32_t rs[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (vs[k] > 0.0f) {
-          const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(rs[k]), vs[k]));
-          if (bits < best_key) { best_key = bits; best_id = 4u * q + k; }
-        }
-      }
-    }
-    warp_argmin(best_key, best_id);
-    if (best_id == 0xFFFFFFFFu) return -1;
-    return 4 * c.q0 + (int64_t)best_id;
-  }
-  // strips
-  const uint32_t nsuper = (c.nq + fw::kQuadsPerSuper - 1) / fw::kQuadsPerSuper;
-  for (uint32_t s = 0; s < nsuper; ++s) {
-    const uint32_t base = s * fw::kQuadsPerSuper + lane;
-    float S[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t q = base + 32u * j;
-      S[j] = q < c.nq ? sum4(load_bias4<APP>(a, c, q)) : 0.0f;
-    }
-    const float W = __fadd_rn(__fadd_rn(S[0], S[1]), __fadd_rn(S[2], S[3]));
-    if (W > 0.0f) {
-      const uint32_t B = s * 32u + lane;
-      const fw::Philox4 r = fw::philox4x32_10(B, c1, qlo, qhi, a.k0, a.k1);
-      const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(r.x), W));
-      if (bits < best_key) { best_key = bits; best_id = B; }
-    }
-  }
-  warp_argmin(best_key, best_id);
-  if (best_id == 0xFFFFFFFFu) return -1;
-  // inverse-CDF pick inside the winning strip (every lane computes the same)
-  const uint32_t B = best_id;
-  const uint32_t qb = (B >> 5) * fw::kQuadsPerSuper + (B & 31u);
-  const fw::Philox4 r = fw::philox4x32_10(B, c1, qlo, qhi, a.k0, a.k1);
-  float4 v[4];
-  float S[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t q = qb + 32u * j;
-    v[j] = q < c.nq ? load_bias4<APP>(a, c, q) : make_float4(0.f, 0.f, 0.f, 0.f);
-    S[j] = sum4(v[j]);
-  }
-  const float W = __fadd_rn(__fadd_rn(S[0], S[1]), __fadd_rn(S[2], S[3]));
-  const float t = __fmul_rn((float)(r.y >> 8) * 0x1p-24f, W);
-  float acc = 0.0f;
-  int64_t last = -1, chosen = -1;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (vs[k] > 0.0f && chosen < 0) {
-        last = 4 * (c.q0 + qb + 32u * j) + k;
-        acc = __fadd_rn(acc, vs[k]);
-        if (acc > t) chosen = last;
-      }
-    }
-  }
-  return chosen >= 0 ? chosen : last;
-}
-
-template <int APP, int MODE, typename OffT>
-__global__ void __launch_bounds__(kThreads) walk_kernel(const __grid_constant__ WalkArgs a) {
-  extern __shared__ uint32_t s_hist[];
-  const int lane = threadIdx.x & 31;
-  const OffT* __restrict__ xadj = static_cast<const OffT*>(a.xadj);
-  const int64_t D = (int64_t)a.d + 1;
-  if (a.hist_in_smem) {
-    for (int z = threadIdx.x; z <= a.d; z += blockDim.x) s_hist[z] = 0u;
-    __syncthreads();
-  }
-  unsigned long long my_steps = 0, my_scanned = 0;
-  uint32_t status = 0;
-
-  for (;;) {
-    long long first = 0;
-    if (lane == 0) first = (long long)atomicAdd(a.scratch + kSlotCounter, (unsigned long long)kClaim);
-    first = __shfl_sync(0xFFFFFFFFu, first, 0);
-    if (first >= a.n) break;
-    const long long stop = first + kClaim < a.n ? first + kClaim : a.n;
-    for (long long qi = first; qi < stop; ++qi) {
-      const uint64_t qid = a.qid_base + (uint64_t)qi;
-      const uint32_t qlo = (uint32_t)qid, qhi = (uint32_t)(qid >> 32);
-      int32_t* __restrict__ row_out = a.result + qi * D;
-      int32_t cur = __ldg(a.starts + qi);
-      if (lane == 0) row_out[0] = cur;
-      StepCtx c;
-      c.prev = -1; c.pb = 0; c.pe = 0; c.want = 0;
-      int k = 0;
-      if (cur < 0 || (int64_t)cur >= a.V) {
-        status |= FW_STATUS_BAD_START;
-      } else {
-        while (k < a.d) {
-          const int64_t b = (int64_t)__ldg(xadj + cur), e = (int64_t)__ldg(xadj + cur + 1);
-          if (e <= b) break;
-          c.q0 = b >> 2;
-          c.nq = (uint32_t)(((e + 3) >> 2) - c.q0);
-          c.head = (uint32_t)(b - 4 * c.q0);
-          c.tail = (uint32_t)(e - 4 * c.q0);
-          if (APP == FW_APP_METAPATH) c.want = a.schema[k % a.schema_len];
-          const int64_t sel = sample_row_warp<APP, MODE>(a, c, (uint32_t)k | (fw::kPurposeScan << 28),
-                                                         qlo, qhi, lane);
-          if (sel < 0) break;  // include/walker.cuh:1373-1374
-          const int32_t nxt = __ldg(a.adj + sel);
-          if (nxt < 0 || (int64_t)nxt >= a.V) { status |= FW_STATUS_BAD_NEIGHBOR; break; }
-          if (lane == 0) row_out[k + 1] = nxt;  // include/walker.cuh:1380-1381
-          my_scanned += (unsigned long long)(e - b);
-          c.prev = cur; c.pb = b; c.pe = e;  // include/gpu_task.cuh:70-77
-          cur = nxt;
-          ++k;
-          if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
-            const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(k - 1) | (fw::kPurposeStop << 28),
-                                                    qlo, qhi, a.k0, a.k1);
-            if (r.x < a.tp_thresh) break;
-          }
-        }
-      }
-      for (int z = k + 1 + lane; z <= a.d; z += 32) row_out[z] = -1;
-      my_steps += (unsigned long long)k;
-      if (lane == 0) {
-        if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
-        else atomicAdd(a.scratch + kSlotHist + k, 1ull);
-      }
-    }
-  }
-  if (lane == 0) {
-    if (my_steps) atomicAdd(a.scratch + kSlotSteps, my_steps);
-    if (my_scanned) atomicAdd(a.scratch + kSlotScanned, my_scanned);
-    if (status) atomicOr(a.scratch + kSlotStatus, (unsigned long long)status);
-  }
-  if (a.hist_in_smem) {
-    __syncthreads();
-    for (int z = threadIdx.x; z <= a.d; z += blockDim.x)
-      if (s_hist[z]) atomicAdd(a.scratch + kSlotHist + z, (unsigned long long)s_hist[z]);
-  }
-}
-
-using KernelFn = void (*)(const WalkArgs);
-
-template <int APP, int MODE>
-KernelFn pick_off(int xadj_bits) {
-  return xadj_bits == 64 ? (KernelFn)walk_kernel<APP, MODE, int64_t>
-                         : (KernelFn)walk_kernel<APP, MODE, uint32_t>;
-}
-template <int APP>
-KernelFn pick_mode(int mode, int xadj_bits) {
-  return mode == FW_GROUP_EDGE ? pick_off<APP, FW_GROUP_EDGE>(xadj_bits)
-                               : pick_off<APP, FW_GROUP_STRIP>(xadj_bits);
-}
-KernelFn pick_kernel(int app, int mode, int xadj_bits) {
-  switch (app) {
-    case FW_APP_DEEPWALK: return pick_mode<FW_APP_DEEPWALK>(mode, xadj_bits);
-    case FW_APP_PPR: return pick_mode<FW_APP_PPR>(mode, xadj_bits);
-    case FW_APP_NODE2VEC: return pick_mode<FW_APP_NODE2VEC>(mode, xadj_bits);
-    default: return pick_mode<FW_APP_METAPATH>(mode, xadj_bits);
-  }
-}
-
-}  // namespace
 
 // ---------------------------------------------------------------------------
 // Engine
@@ -313,6 +35,7 @@ struct fw_engine {
   int sms = 0;
   int64_t V = 0, E = 0;
   int xadj_bits = 32;
+  bool clean_weights = false;  // every weight is >= 0 and not NaN: the kernels skip the clamp
   void* d_xadj = nullptr;
   int32_t* d_adj = nullptr;
   float* d_weight = nullptr;
@@ -401,8 +124,10 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   a.schema_len = p->app == FW_APP_METAPATH ? p->schema_len : 1;
   for (int i = 0; i < kMaxSchema; ++i) a.schema[i] = (p->app == FW_APP_METAPATH && i < p->schema_len) ? p->schema[i] : 0;
   const int mode = p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode;
-  KernelFn fn = pick_kernel(p->app, mode, e->xadj_bits);
-  const size_t smem = a.hist_in_smem ? (size_t)(p->d + 1) * 4 : 0;
+  KernelFn fn = pick_kernel(p->app, mode, e->clean_weights, e->xadj_bits);
+  const size_t smem = kernel_smem_bytes(p->app, mode, p->d, a.hist_in_smem != 0);
+  if (smem > 48 * 1024)
+    FW_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
   FW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
   if (per_sm < 1) return fw::fail(FW_ERR_CUDA, "walk kernel does not fit on an SM");
@@ -474,6 +199,11 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
     FW_CUDA(cudaMemcpy(e->d_xadj, g->xadj, (size_t)(g->xadj_bits / 8) * (size_t)(g->V + 1), cudaMemcpyHostToDevice));
     int r = upload_edges(g->adj, g->E, &e->d_adj);
     if (!r && want_w) r = upload_edges(g->weight, g->E, &e->d_weight);
+    if (want_w) {
+      bool clean = true;
+      for (int64_t i = 0; i < g->E && clean; ++i) clean = g->weight[i] >= 0.0f;
+      e->clean_weights = clean;
+    }
     if (!r && want_l) r = upload_edges(g->label, g->E, &e->d_label);
     if (r) return r;
     FW_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
@@ -734,8 +464,11 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
   a.schema_len = p->app == FW_APP_METAPATH ? p->schema_len : 1;
   for (int i = 0; i < kMaxSchema; ++i)
     a.schema[i] = (p->app == FW_APP_METAPATH && i < p->schema_len) ? p->schema[i] : 0;
-  KernelFn fn = pick_kernel(p->app, p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode, xadj_bits);
-  const size_t smem = (size_t)(p->d + 1) * 4;
+  const int mode = p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode;
+  KernelFn fn = pick_kernel(p->app, mode, /*clean=*/false, xadj_bits);  // caller's weights: not inspected
+  const size_t smem = kernel_smem_bytes(p->app, mode, p->d, true);
+  if (smem > 48 * 1024)
+    FW_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0, sms = 0;
   FW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
   FW_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
