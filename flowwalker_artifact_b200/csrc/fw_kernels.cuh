@@ -275,18 +275,20 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   }
 
   // ---- strips ----
+  // Philox block g of lane l (counter word 0 = g*32 + l) serves supergroups 3g, 3g+1, 3g+2
+  // (words 0..2 -> keys) and carries in word 3 the uniform for the in-strip pick.
   const uint32_t nsuper = (c.nq + fw::kQuadsPerSuper - 1) / fw::kQuadsPerSuper;
-  // supergroup s is interior iff it has all its quads and holds neither quad 0 nor quad nq-1
-  auto consider = [&](uint32_t s, float W, const fw::Philox4& r) {
+  uint32_t best_pick = 0u;
+  auto consider = [&](uint32_t s, uint32_t m, float W, const fw::Philox4& r) {
     if (W > 0.0f) {
-      const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(word_of(r, s & 3u)), W));
-      if (bits < best_key) { best_key = bits; best_id = s * 32u + lane; }
+      const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(word_of(r, m)), W));
+      if (bits < best_key) { best_key = bits; best_id = s * 32u + lane; best_pick = r.w; }
     }
   };
-  if (nsuper < kRingMinSuper) {
-    fw::Philox4 r = fw::philox4x32_10((uint32_t)lane, c1, qlo, qhi, a.k0, a.k1);  // nsuper <= 4: one block
+  fw::Philox4 r = fw::philox4x32_10((uint32_t)lane, c1, qlo, qhi, a.k0, a.k1);
+  if (nsuper < kRingMinSuper) {  // at most two supergroups: block 0 covers them
     for (uint32_t s = 0; s < nsuper; ++s)
-      consider(s, strip_weight_global<APP, CLEAN>(a, c, s, lane, false, nullptr), r);
+      consider(s, s, strip_weight_global<APP, CLEAN>(a, c, s, lane, false, nullptr), r);
   } else {
     // first and last supergroups straight from global memory (boundary quads, partial fill);
     // the interior ones through the ring
@@ -305,11 +307,10 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
         }
       }
     }
-    fw::Philox4 r = fw::philox4x32_10((uint32_t)lane, c1, qlo, qhi, a.k0, a.k1);
-    consider(0, strip_weight_global<APP, CLEAN>(a, c, 0, lane, false, nullptr), r);
-    uint32_t t = 0;
+    consider(0, 0, strip_weight_global<APP, CLEAN>(a, c, 0, lane, false, nullptr), r);
+    uint32_t t = 0, m = 1, g = 0;  // stage, s mod 3, s div 3
     for (uint32_t s = first; s < last; ++s) {
-      if ((s & 3u) == 0) r = fw::philox4x32_10((s >> 2) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+      if (m == 0) r = fw::philox4x32_10(g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
       const uint32_t bar = ring.bar + 8u * t;
       float W = 0.0f;
       if (!ring.failed) {
@@ -321,7 +322,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
           ring.failed = true;
         }
       }
-      consider(s, W, r);  // consumes the staged values before the stage is handed back
+      consider(s, m, W, r);  // consumes the staged values before the stage is handed back
       ring.failed = __any_sync(0xFFFFFFFFu, ring.failed);
       // every lane has consumed the stage: refill it with supergroup s + kStages
       if (lane == 0 && !ring.failed && s + kStages < last) {
@@ -332,35 +333,45 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
                    kSuperBytes, bar);
       }
       t = t + 1 == kStages ? 0 : t + 1;
+      if (++m == 3) { m = 0; ++g; }
     }
-    if ((last & 3u) == 0) r = fw::philox4x32_10((last >> 2) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
-    consider(last, strip_weight_global<APP, CLEAN>(a, c, last, lane, false, nullptr), r);
+    if (m == 0) r = fw::philox4x32_10(g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+    consider(last, m, strip_weight_global<APP, CLEAN>(a, c, last, lane, false, nullptr), r);
     if (ring.failed) return 0xFFFFFFFFu;
   }
   warp_argmin(best_key, best_id);
   if (best_id == 0xFFFFFFFFu) return best_id;
-  // inverse-CDF pick inside the winning strip (every lane computes the same)
+  // Inverse-CDF pick inside the winning strip B (every lane computes the same): the
+  // first of its 16 edges whose running sum exceeds u * W.  Zero biases leave the running
+  // sum unchanged, so the count of sums <= u * W is that edge's position.
   const uint32_t B = best_id;
-  const fw::Philox4 r = fw::philox4x32_10(B, step | (fw::kPurposePick << 28), qlo, qhi, a.k0, a.k1);
+  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best_pick, (int)(B & 31u));
+  const uint32_t sB = B >> 5;
   float4 v[4];
-  const float W = strip_weight_global<APP, CLEAN>(a, c, B >> 5, (int)(B & 31u), false, v);
-  const float t = __fmul_rn((float)(r.x >> 8) * 0x1p-24f, W);
-  const uint32_t qb = (B >> 5) * fw::kQuadsPerSuper + (B & 31u);
+  const float W = strip_weight_global<APP, CLEAN>(a, c, sB, (int)(B & 31u), sB > 0 && sB + 1 < nsuper, v);
+  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
+  const uint32_t qb = sB * fw::kQuadsPerSuper + (B & 31u);
   float acc = 0.0f;
-  uint32_t last_pos = 0xFFFFFFFFu, chosen = 0xFFFFFFFFu;
+  uint32_t cnt = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      if (vs[k] > 0.0f && chosen == 0xFFFFFFFFu) {
-        last_pos = 4u * (qb + 32u * j) + k;
-        acc = __fadd_rn(acc, vs[k]);
-        if (acc > t) chosen = last_pos;
-      }
+      acc = __fadd_rn(acc, vs[k]);
+      cnt += acc <= thr ? 1u : 0u;
     }
   }
-  return chosen != 0xFFFFFFFFu ? chosen : last_pos;
+  if (cnt >= 16u) {  // rounding pushed u * W past the sequential total: take the last positive edge
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (vs[k] > 0.0f) cnt = 4u * j + k;
+    }
+  }
+  return 4u * (qb + 32u * (cnt >> 2)) + (cnt & 3u);
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>

@@ -17,16 +17,15 @@ namespace fw {
 // What a Philox block is used for (upper 4 bits of counter word 1).
 constexpr uint32_t kPurposeScan = 0u;  // keys of the row scan
 constexpr uint32_t kPurposeStop = 1u;  // PPR stop test after a step
-constexpr uint32_t kPurposePick = 2u;  // inverse-CDF pick inside the winning strip
 
 // A row [b,e) of the CSR is addressed in aligned quads of 4 edges (16 bytes):
 // quad q covers absolute edges 4*(q0+q) .. +3 with q0 = b>>2.  A supergroup
 // is 128 consecutive quads (2 KB); strip (s,l) holds quads s*128 + j*32 + l,
 // j = 0..3 -- the four 16-byte loads of lane l when a warp sweeps supergroup s.
-// Strip (s,l) has id B = s*32 + l; its key uses word s&3 of the scan block
-// with counter word 0 = (s>>2)*32 + l (one Philox block serves four
-// supergroups of a lane); the pick inside the winning strip uses word 0 of
-// the pick block with counter word 0 = B.
+// Strip (s,l) has id B = s*32 + l; its key uses word s%3 of the scan block
+// with counter word 0 = (s/3)*32 + l (one Philox block serves three
+// supergroups of a lane); word 3 of that block is the uniform for the pick
+// inside the winning strip.
 constexpr int kQuadsPerSuper = 128;
 
 struct Philox4 { uint32_t x, y, z, w; };

@@ -28,8 +28,8 @@
  * W = total bias of the group; the smallest (key, group index) wins.  Group
  * mode 1: one neighbour per group.  Group mode 16: a "strip" of up to 16
  * neighbours (four 16-byte quads 512 bytes apart); the neighbour inside the
- * winning strip is then drawn by inverse CDF with a uniform from a second
- * Philox block.
+ * winning strip is then drawn by inverse CDF with the fourth word of the
+ * strip's Philox block (words 0..2 are the keys of three strips).
  *
  * Floating point: only +, *, /, fmaf (correctly rounded on host and device);
  * build with -ffp-contract=off.
@@ -49,7 +49,6 @@
 
 #define FWO_PURPOSE_SCAN 0u
 #define FWO_PURPOSE_STOP 1u
-#define FWO_PURPOSE_PICK 2u
 
 /* ---- Philox4x32-10 (Salmon et al., SC'11), restated ---- */
 void fwo_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2],
@@ -205,20 +204,20 @@ static int64_t sample_row(const fwo_ctx* c, int64_t b, int64_t e, int k,
       float W = (S[0] + S[1]) + (S[2] + S[3]);
       if (!(W > 0.0f)) continue;
       uint32_t B = (uint32_t)(s * 32 + l);
-      ctr[0] = (uint32_t)((s >> 2) * 32 + l);  /* one block serves supergroups 4t..4t+3 of lane l */
+      ctr[0] = (uint32_t)((s / 3) * 32 + l);  /* one block serves supergroups 3g..3g+2 of lane l */
       fwo_philox4x32_10(ctr, c->key, r);
-      float key = fwo_exp_key(r[s & 3]) / W;
+      float key = fwo_exp_key(r[s % 3]) / W;
       uint64_t packed = ((uint64_t)f2u(key) << 32) | B;
       if (packed < best) best = packed;
     }
   }
   if (best == ~(uint64_t)0) return -1;
-  /* inverse-CDF pick inside the winning strip, from its own pick block */
+  /* inverse-CDF pick inside the winning strip: word 3 of the strip's scan block;
+   * the first edge (canonical order) whose running sum exceeds u * W */
   uint32_t B = (uint32_t)best;
   int64_t s = B >> 5;
   int l = (int)(B & 31u);
-  ctr[0] = B;
-  ctr[1] = (uint32_t)k | (FWO_PURPOSE_PICK << 28);
+  ctr[0] = (uint32_t)((s / 3) * 32 + l);
   fwo_philox4x32_10(ctr, c->key, r);
   float w16[16];
   int64_t i16[16];
@@ -233,7 +232,7 @@ static int64_t sample_row(const fwo_ctx* c, int64_t b, int64_t e, int k,
     S[j] = (w16[4 * j] + w16[4 * j + 1]) + (w16[4 * j + 2] + w16[4 * j + 3]);
   }
   float W = (S[0] + S[1]) + (S[2] + S[3]);
-  float u = (float)(r[0] >> 8) * 0x1p-24f;
+  float u = (float)(r[3] >> 8) * 0x1p-24f;
   float t = u * W;
   float acc = 0.f;
   int64_t last = -1;
