@@ -42,7 +42,8 @@ _lib = None
 
 
 def lib_path():
-    return os.path.join(_HERE, "libflowwalker.so")
+    """Path of the shared library; FLOWWALKER_LIB overrides the in-tree build."""
+    return os.environ.get("FLOWWALKER_LIB") or os.path.join(_HERE, "libflowwalker.so")
 
 
 def lib():

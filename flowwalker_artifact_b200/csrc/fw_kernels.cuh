@@ -24,7 +24,13 @@ constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = 32 * kWarpsPerCta;
 constexpr int kClaim = 4;                // queries claimed per atomic
 constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared memory up to this d+1
-constexpr int kStages = 2;               // ring depth per warp
+#ifndef FW_STAGES
+#define FW_STAGES 2
+#endif
+#ifndef FW_MIN_BLOCKS
+#define FW_MIN_BLOCKS 5
+#endif
+constexpr int kStages = FW_STAGES;       // ring depth per warp
 constexpr uint32_t kSuperBytes = 16u * fw::kQuadsPerSuper;  // 2 KB
 constexpr uint32_t kRingMinSuper = 3;    // rows with at least this many supergroups use the ring
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls of an mbarrier before giving up
@@ -119,12 +125,10 @@ __device__ __forceinline__ bool row_contains(const int32_t* __restrict__ adj, in
 }
 
 // Biases of the four edges of quad q from its raw 16 bytes (`nb`: the four
-// neighbour ids, node2vec only).  `edges`: the quad may be the first or last of
-// the row, whose edges outside [head, tail) get bias 0.  CLEAN: the weights are
-// known to be >= 0 and not NaN, so the clamp is skipped.
+// neighbour ids, node2vec only).  Edges outside the row are NOT masked here.
+// CLEAN: the weights are known to be >= 0 and not NaN, so the clamp is skipped.
 template <int APP, bool CLEAN>
-__device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c, int4 raw, int4 nb,
-                                            uint32_t q, bool edges) {
+__device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c, int4 raw, int4 nb, uint32_t q) {
   float4 v;
   if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
     v.x = raw.x == c.want ? 1.0f : 0.0f;
@@ -147,14 +151,16 @@ __device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c,
     }
     if (!CLEAN) { v.x = pos(v.x); v.y = pos(v.y); v.z = pos(v.z); v.w = pos(v.w); }
   }
-  if (edges && (q == 0 || q + 1 == c.nq)) {
-    const uint32_t r = 4u * q;
-    if (r + 0 < c.head || r + 0 >= c.tail) v.x = 0.0f;
-    if (r + 1 < c.head || r + 1 >= c.tail) v.y = 0.0f;
-    if (r + 2 < c.head || r + 2 >= c.tail) v.z = 0.0f;
-    if (r + 3 < c.head || r + 3 >= c.tail) v.w = 0.0f;
-  }
   return v;
+}
+
+// Zeroes the edges of quad q that lie outside [head, tail) (relative edge indices).
+__device__ __forceinline__ void mask_quad(float4& v, uint32_t q, uint32_t head, uint32_t tail) {
+  const uint32_t x = 4u * q - head, span = tail - head;  // unsigned wrap makes "below head" huge
+  v.x = x < span ? v.x : 0.0f;
+  v.y = x + 1u < span ? v.y : 0.0f;
+  v.z = x + 2u < span ? v.z : 0.0f;
+  v.w = x + 3u < span ? v.w : 0.0f;
 }
 
 __device__ __forceinline__ float sum4(const float4 v) {
@@ -164,59 +170,34 @@ __device__ __forceinline__ float sum_strip(const float S[4]) {
   return __fadd_rn(__fadd_rn(S[0], S[1]), __fadd_rn(S[2], S[3]));
 }
 
-// Total bias of lane `lane`'s strip of supergroup s, read from global memory.
-// `interior`: all 128 quads exist and none is a boundary quad.
+// Quad q of the row from global memory, masked when `boundary` (warp-uniform: the
+// 32-quad block holds the first or the last quad of the row) says it may need it.
 template <int APP, bool CLEAN>
-__device__ __forceinline__ float strip_weight_global(const WalkArgs& a, const StepCtx& c, uint32_t s,
-                                                     int lane, bool interior, float4* keep) {
-  const uint32_t base = s * fw::kQuadsPerSuper + lane;
+__device__ __forceinline__ float4 load_quad(const WalkArgs& a, const StepCtx& c, uint32_t q, bool boundary) {
   const int4 zero = make_int4(0, 0, 0, 0);
-  float S[4];
-  if (interior) {
-    int4 raw[4], nb[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) raw[j] = __ldg(c.prim + base + 32u * j);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? __ldg(c.sec + base + 32u * j) : zero;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float4 v = quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], base + 32u * j, false);
-      if (keep) keep[j] = v;
-      S[j] = sum4(v);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t q = base + 32u * j;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (s * fw::kQuadsPerSuper + 32u * j < c.nq) {  // warp-uniform: skip empty quarter sweeps
-        if (q < c.nq) {
-          const int4 raw = __ldg(c.prim + q);
-          const int4 nb = APP == FW_APP_NODE2VEC ? __ldg(c.sec + q) : zero;
-          v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, true);
-        }
-      }
-      if (keep) keep[j] = v;
-      S[j] = sum4(v);
-    }
-  }
-  return sum_strip(S);
+  const bool valid = q < c.nq;
+  const int4 raw = valid ? __ldg(c.prim + q) : zero;
+  const int4 nb = (APP == FW_APP_NODE2VEC && valid) ? __ldg(c.sec + q) : zero;
+  float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q);
+  if (boundary) mask_quad(v, q, c.head, c.tail);
+  return v;
 }
 
-// Same from a staged supergroup in shared memory (interior supergroups only).
+// Lane `lane`'s strip of supergroup s from global memory: total bias, the four
+// quads optionally kept.  Blocks past the end of the row are skipped as a warp.
 template <int APP, bool CLEAN>
-__device__ __forceinline__ float strip_weight_staged(const WalkArgs& a, const StepCtx& c, uint32_t s, int lane,
-                                                     const int4* st_prim, const int4* st_sec) {
-  const uint32_t base = s * fw::kQuadsPerSuper + lane;
-  const int4 zero = make_int4(0, 0, 0, 0);
-  int4 raw[4], nb[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) raw[j] = st_prim[lane + 32 * j];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? st_sec[lane + 32 * j] : zero;
+__device__ __forceinline__ float strip_global(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t lane,
+                                              float4* keep) {
+  const uint32_t last_blk = (c.nq - 1u) >> 5;
   float S[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) S[j] = sum4(quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], base + 32u * j, false));
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t blk = 4u * s + j;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (blk <= last_blk) v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, blk == 0u || blk == last_blk);
+    if (keep) keep[j] = v;
+    S[j] = sum4(v);
+  }
   return sum_strip(S);
 }
 
@@ -227,8 +208,29 @@ __device__ __forceinline__ void warp_argmin(uint32_t& key, uint32_t& id) {
   key = m;
 }
 
-__device__ __forceinline__ uint32_t word_of(const fw::Philox4& r, uint32_t k) {
-  return k == 0 ? r.x : k == 1 ? r.y : k == 2 ? r.z : r.w;
+// A lane's best candidate so far.
+struct Best {
+  uint32_t key, id, pick;
+};
+
+// Exact test of one strip: key = E(x) / W.
+__device__ __forceinline__ void offer(Best& b, uint32_t x, uint32_t pick_word, float W, uint32_t id) {
+  if (W > 0.0f) {
+    const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(x), W));
+    if (bits < b.key) { b.key = bits; b.id = id; b.pick = pick_word; }
+  }
+}
+
+// The same test behind a cheap filter, for the long sweep: E >= clz(x) and, when
+// clz(x) == 0, E >= 0.72 * m, so a strip whose lower bound already exceeds
+// (best key so far) * W cannot win and its exact key (polynomial + division) is never
+// formed.  `bound` may be stale or NaN (nothing found yet): the comparison then lets
+// the candidate through.
+__device__ __forceinline__ void offer_filtered(Best& b, uint32_t x, uint32_t pick_word, float W, uint32_t id,
+                                               float bound) {
+  const int g = __clz((int)x);
+  const float lower = g ? (float)g : __fmul_rn((float)(x << 1), 0.72f * 0x1p-32f);
+  if (W > 0.0f && !(lower > __fmul_rn(__fmul_rn(bound, W), 1.000001f))) offer(b, x, pick_word, W, id);
 }
 
 // Per-warp ring state.
@@ -244,21 +246,89 @@ __device__ __forceinline__ constexpr uint32_t stage_bytes() {
   return APP == FW_APP_NODE2VEC ? 2u * kSuperBytes : kSuperBytes;
 }
 
+// Inverse-CDF pick among the 16 biases of a strip in canonical order (quad j, edge k):
+// the first edge whose running sum exceeds thr.  Zero biases leave the running sum
+// unchanged, so the count of sums <= thr is that edge's position; 16 means rounding
+// pushed thr past the sequential total, and the last positive edge is taken.
+__device__ __forceinline__ uint32_t pick_in_strip(const float4 v[4], float thr) {
+  float acc = 0.0f;
+  uint32_t cnt = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc = __fadd_rn(acc, vs[k]);
+      cnt += acc <= thr ? 1u : 0u;
+    }
+  }
+  if (cnt >= 16u) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (vs[k] > 0.0f) cnt = 4u * j + k;
+    }
+  }
+  return cnt;
+}
+
+// One interior supergroup s from stage T of the ring: wait for its copy, reduce the lane's
+// strip, hand the stage back (refill with supergroup s + kStages), then test the strip's key
+// (random word x, pick word pw).  False when the wait ran out.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ bool ring_step(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t last,
+                                          uint32_t lane, Ring& ring, const unsigned char* ring_ptr, uint32_t x,
+                                          uint32_t pw, Best& best, const uint32_t T) {
+  constexpr uint32_t kSB = stage_bytes<APP>();
+  const uint32_t bar = ring.bar + 8u * T;
+  bool ok = mbar_try_wait(bar, (ring.parity >> T) & 1u) != 0;
+  if (!ok) ok = mbar_wait(bar, (ring.parity >> T) & 1u);
+  ring.parity ^= 1u << T;
+  const int4* st = reinterpret_cast<const int4*>(ring_ptr + T * kSB);
+  const int4 zero = make_int4(0, 0, 0, 0);
+  int4 raw[4], nb[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) raw[j] = st[lane + 32 * j];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? st[fw::kQuadsPerSuper + lane + 32 * j] : zero;
+  float S[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    S[j] = sum4(quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], s * fw::kQuadsPerSuper + lane + 32u * j));
+  const float W = sum_strip(S);
+  // Every lane's W is formed (its staged values are consumed) before the stage is refilled.
+  if (!__all_sync(0xFFFFFFFFu, ok && W >= 0.0f)) return false;
+  if (lane == 0 && s + kStages < last) {
+    mbar_expect_tx(bar, kSB);
+    bulk_g2s(ring.data + T * kSB, c.prim + (size_t)(s + kStages) * fw::kQuadsPerSuper, kSuperBytes, bar);
+    if (APP == FW_APP_NODE2VEC)
+      bulk_g2s(ring.data + T * kSB + kSuperBytes, c.sec + (size_t)(s + kStages) * fw::kQuadsPerSuper, kSuperBytes,
+               bar);
+  }
+  // the warp-wide best so far bounds every lane's candidates
+  const float bound = __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key));
+  offer_filtered(best, x, pw, W, s * 32u + lane, bound);
+  return true;
+}
+
 // One weighted pick in the row described by c, by one warp.  Returns the
 // edge index relative to quad 0 of the row, or 0xFFFFFFFF when no edge has
 // positive bias.
 template <int APP, int MODE, bool CLEAN>
 __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const StepCtx& c, uint32_t step,
-                                                    uint32_t qlo, uint32_t qhi, int lane, Ring& ring,
+                                                    uint32_t qlo, uint32_t qhi, uint32_t lane, Ring& ring,
                                                     const unsigned char* ring_ptr) {
   const uint32_t c1 = step | (fw::kPurposeScan << 28);
-  uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu;
   const int4 zero = make_int4(0, 0, 0, 0);
   if (MODE == FW_GROUP_EDGE) {
+    uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu;
     for (uint32_t q = lane; q < c.nq; q += 32) {
       const int4 raw = __ldg(c.prim + q);
       const int4 nb = APP == FW_APP_NODE2VEC ? __ldg(c.sec + q) : zero;
-      const float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, true);
+      float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q);
+      mask_quad(v, q, c.head, c.tail);
       const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.k0, a.k1);
       const float vs[4] = {v.x, v.y, v.z, v.w};
       const uint32_t rs[4] = {r.x, r.y, r.z, r.w};
@@ -277,27 +347,41 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   // ---- strips ----
   // Philox block g of lane l (counter word 0 = g*32 + l) serves supergroups 3g, 3g+1, 3g+2
   // (words 0..2 -> keys) and carries in word 3 the uniform for the in-strip pick.
+  Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u};
+  fw::Philox4 r = fw::philox4x32_10(lane, c1, qlo, qhi, a.k0, a.k1);
+
+  if (c.nq <= 32u) {
+    // Short row: one quad per lane, strip = that quad; the winner's quad travels by shuffle.
+    float4 v = load_quad<APP, CLEAN>(a, c, lane, true);
+    offer(best, r.x, r.w, sum4(v), lane);
+    warp_argmin(best.key, best.id);
+    if (best.id == 0xFFFFFFFFu) return best.id;
+    const int src = (int)best.id;
+    v.x = __shfl_sync(0xFFFFFFFFu, v.x, src);
+    v.y = __shfl_sync(0xFFFFFFFFu, v.y, src);
+    v.z = __shfl_sync(0xFFFFFFFFu, v.z, src);
+    v.w = __shfl_sync(0xFFFFFFFFu, v.w, src);
+    const uint32_t pick = __shfl_sync(0xFFFFFFFFu, r.w, src);
+    const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, sum4(v));
+    const float p0 = v.x, p1 = __fadd_rn(p0, v.y), p2 = __fadd_rn(p1, v.z), p3 = __fadd_rn(p2, v.w);
+    uint32_t cnt = (p0 <= thr ? 1u : 0u) + (p1 <= thr ? 1u : 0u) + (p2 <= thr ? 1u : 0u) + (p3 <= thr ? 1u : 0u);
+    if (cnt >= 4u) cnt = v.w > 0.0f ? 3u : v.z > 0.0f ? 2u : v.y > 0.0f ? 1u : 0u;
+    return 4u * (uint32_t)src + cnt;
+  }
+
   const uint32_t nsuper = (c.nq + fw::kQuadsPerSuper - 1) / fw::kQuadsPerSuper;
-  uint32_t best_pick = 0u;
-  auto consider = [&](uint32_t s, uint32_t m, float W, const fw::Philox4& r) {
-    if (W > 0.0f) {
-      const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(word_of(r, m)), W));
-      if (bits < best_key) { best_key = bits; best_id = s * 32u + lane; best_pick = r.w; }
-    }
-  };
-  fw::Philox4 r = fw::philox4x32_10((uint32_t)lane, c1, qlo, qhi, a.k0, a.k1);
   if (nsuper < kRingMinSuper) {  // at most two supergroups: block 0 covers them
-    for (uint32_t s = 0; s < nsuper; ++s)
-      consider(s, s, strip_weight_global<APP, CLEAN>(a, c, s, lane, false, nullptr), r);
+    offer(best, r.x, r.w, strip_global<APP, CLEAN>(a, c, 0, lane, nullptr), lane);
+    if (nsuper > 1) offer(best, r.y, r.w, strip_global<APP, CLEAN>(a, c, 1, lane, nullptr), 32u + lane);
   } else {
     // first and last supergroups straight from global memory (boundary quads, partial fill);
-    // the interior ones through the ring
-    const uint32_t first = 1, last = nsuper - 1;  // interior = [first, last)
+    // the interior ones [1, last) through the ring
+    const uint32_t last = nsuper - 1;
     constexpr uint32_t kSB = stage_bytes<APP>();
     if (lane == 0) {
 #pragma unroll
       for (uint32_t t = 0; t < kStages; ++t) {
-        const uint32_t s = first + t;
+        const uint32_t s = 1u + t;
         if (s < last) {
           const uint32_t bar = ring.bar + 8u * t;
           mbar_expect_tx(bar, kSB);
@@ -307,78 +391,41 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
         }
       }
     }
-    consider(0, 0, strip_weight_global<APP, CLEAN>(a, c, 0, lane, false, nullptr), r);
-    uint32_t t = 0, m = 1, g = 0;  // stage, s mod 3, s div 3
-    for (uint32_t s = first; s < last; ++s) {
-      if (m == 0) r = fw::philox4x32_10(g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
-      const uint32_t bar = ring.bar + 8u * t;
-      float W = 0.0f;
-      if (!ring.failed) {
-        if (mbar_wait(bar, (ring.parity >> t) & 1u)) {
-          ring.parity ^= 1u << t;
-          const int4* st = reinterpret_cast<const int4*>(ring_ptr + t * kSB);
-          W = strip_weight_staged<APP, CLEAN>(a, c, s, lane, st, st + fw::kQuadsPerSuper);
-        } else {
-          ring.failed = true;
-        }
+    offer(best, r.x, r.w, strip_global<APP, CLEAN>(a, c, 0, lane, nullptr), lane);
+    uint32_t g = 0, t = 0, m = 1;  // Philox block, ring stage, s mod 3
+    // Kept rolled on purpose: an unrolled sweep measured slower (instruction cache shared by
+    // 40 warps that sit at different places of the kernel).
+#pragma unroll 1
+    for (uint32_t s = 1; s < last; ++s) {
+      if (m == 0) r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+      if (!ring_step<APP, CLEAN>(a, c, s, last, lane, ring, ring_ptr, m == 0 ? r.x : m == 1 ? r.y : r.z, r.w,
+                                 best, t)) {
+        ring.failed = true;
+        return 0xFFFFFFFFu;
       }
-      consider(s, m, W, r);  // consumes the staged values before the stage is handed back
-      ring.failed = __any_sync(0xFFFFFFFFu, ring.failed);
-      // every lane has consumed the stage: refill it with supergroup s + kStages
-      if (lane == 0 && !ring.failed && s + kStages < last) {
-        mbar_expect_tx(bar, kSB);
-        bulk_g2s(ring.data + t * kSB, c.prim + (size_t)(s + kStages) * fw::kQuadsPerSuper, kSuperBytes, bar);
-        if (APP == FW_APP_NODE2VEC)
-          bulk_g2s(ring.data + t * kSB + kSuperBytes, c.sec + (size_t)(s + kStages) * fw::kQuadsPerSuper,
-                   kSuperBytes, bar);
-      }
-      t = t + 1 == kStages ? 0 : t + 1;
-      if (++m == 3) { m = 0; ++g; }
+      t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
+      m = m == 2u ? 0u : m + 1u;
     }
-    if (m == 0) r = fw::philox4x32_10(g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
-    consider(last, m, strip_weight_global<APP, CLEAN>(a, c, last, lane, false, nullptr), r);
-    if (ring.failed) return 0xFFFFFFFFu;
+    if (m == 0) r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+    offer(best, m == 0 ? r.x : m == 1 ? r.y : r.z, r.w, strip_global<APP, CLEAN>(a, c, last, lane, nullptr),
+          last * 32u + lane);
   }
-  warp_argmin(best_key, best_id);
-  if (best_id == 0xFFFFFFFFu) return best_id;
-  // Inverse-CDF pick inside the winning strip B (every lane computes the same): the
-  // first of its 16 edges whose running sum exceeds u * W.  Zero biases leave the running
-  // sum unchanged, so the count of sums <= u * W is that edge's position.
-  const uint32_t B = best_id;
-  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best_pick, (int)(B & 31u));
-  const uint32_t sB = B >> 5;
+  warp_argmin(best.key, best.id);
+  if (best.id == 0xFFFFFFFFu) return best.id;
+  // pick inside the winning strip B (every lane computes the same)
+  const uint32_t B = best.id;
+  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u));
   float4 v[4];
-  const float W = strip_weight_global<APP, CLEAN>(a, c, sB, (int)(B & 31u), sB > 0 && sB + 1 < nsuper, v);
-  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
-  const uint32_t qb = sB * fw::kQuadsPerSuper + (B & 31u);
-  float acc = 0.0f;
-  uint32_t cnt = 0;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      acc = __fadd_rn(acc, vs[k]);
-      cnt += acc <= thr ? 1u : 0u;
-    }
-  }
-  if (cnt >= 16u) {  // rounding pushed u * W past the sequential total: take the last positive edge
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (vs[k] > 0.0f) cnt = 4u * j + k;
-    }
-  }
-  return 4u * (qb + 32u * (cnt >> 2)) + (cnt & 3u);
+  const float W = strip_global<APP, CLEAN>(a, c, B >> 5, B & 31u, v);
+  const uint32_t cnt = pick_in_strip(v, __fmul_rn((float)(pick >> 8) * 0x1p-24f, W));
+  return 4u * ((B >> 5) * fw::kQuadsPerSuper + (B & 31u) + 32u * (cnt >> 2)) + (cnt & 3u);
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
-__global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_APP_NODE2VEC ? 5 : 2) walk_kernel(const __grid_constant__ WalkArgs a) {
+__global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_APP_NODE2VEC ? FW_MIN_BLOCKS : 2) walk_kernel(const __grid_constant__ WalkArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_STRIP ? kStages * stage_bytes<APP>() : 0u;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
@@ -448,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
           }
         }
       }
-      for (int z = k + 1 + lane; z <= a.d; z += 32) row_out[z] = -1;
+      for (int z = k + 1 + (int)lane; z <= a.d; z += 32) row_out[z] = -1;
       my_steps += (unsigned long long)k;
       if (lane == 0) {
         if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
