@@ -27,6 +27,9 @@ constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared
 #ifndef FW_STAGES
 #define FW_STAGES 2
 #endif
+#ifndef FW_N2V_MIN_BLOCKS
+#define FW_N2V_MIN_BLOCKS 3
+#endif
 #ifndef FW_MIN_BLOCKS
 #define FW_MIN_BLOCKS 5
 #endif
@@ -68,6 +71,10 @@ struct StepCtx {
   int32_t prev;      // previous vertex or -1
   int64_t pb, pe;    // row of prev (node2vec)
   int32_t want;      // label wanted (MetaPath)
+  // node2vec: where in prev's row the next 32-quad block's search starts (blocks of a row
+  // are visited in ascending order, rows are sorted)
+  mutable int64_t from;
+  uint32_t* flags;  // 32 words of shared memory owned by this warp
 };
 
 // ---- PTX wrappers: mbarrier + bulk async copy (TMA, no multicast) ----
@@ -124,11 +131,137 @@ __device__ __forceinline__ bool row_contains(const int32_t* __restrict__ adj, in
   return false;
 }
 
+// Warp-cooperative lower bound in the sorted range adj[L, R): first index whose value is
+// >= target (R if none).  Each round the 32 lanes probe 32 evenly spaced pivots and one
+// ballot keeps 1/32 of the range, so a row of 10^6 neighbours takes four rounds where the
+// reference's per-thread search (include/gpu_graph.cuh:97-112) takes twenty dependent loads
+// per candidate.  All lanes must call it with the same arguments.
+__device__ __forceinline__ int64_t warp_lower_bound(const int32_t* __restrict__ adj, int64_t L, int64_t R,
+                                                    int32_t target, uint32_t lane) {
+  while (R - L > 32) {
+    const int64_t step = (R - L + 31) >> 5;
+    int64_t idx = L + (int64_t)(lane + 1u) * step - 1;
+    if (idx > R - 1) idx = R - 1;
+    const uint32_t below = __ballot_sync(0xFFFFFFFFu, __ldg(adj + idx) < target);
+    const int cnt = __popc(below);  // pivots are ascending: `below` is a prefix of ones
+    if (cnt == 32) return R;        // the last pivot is adj[R-1]
+    const int64_t nl = L + (int64_t)cnt * step;
+    int64_t nr = nl + step;
+    if (nr > R) nr = R;
+    L = nl;
+    R = nr;
+  }
+  const int32_t v = L + lane < R ? __ldg(adj + L + lane) : 0x7FFFFFFF;
+  return L + __popc(__ballot_sync(0xFFFFFFFFu, v < target && L + lane < R));
+}
+
+constexpr int64_t kN2vStreamMax = 1024;  // windows up to this many entries are streamed, larger ones probed
+
+// node2vec membership for one 32-quad block: which of this lane's four neighbour ids `nb`
+// (quad q) occur in the previous vertex's sorted row.  Returns a 4-bit mask.
+//
+// Blocks of a row are visited in ascending order and both rows are sorted, so the part of
+// prev's row that matters starts where the previous block's part ended (c.from) and ends at
+// the first entry above the block's largest id.  That window is streamed 32 entries at a
+// time (one coalesced load per round); every entry looks up its position among the block's
+// 128 ids, which stay in registers, with a binary search by shuffles, and flags a match in
+// shared memory for the lane that holds it.  Cost: about two instructions per window entry
+// and no dependent global loads per candidate, where the reference probes prev's whole row
+// once per candidate (include/gpu_graph.cuh:97-118).  Windows much longer than the block
+// (prev a far bigger hub than the current vertex) fall back to per-candidate probes inside
+// the window, found by the warp-wide search.  Every lane of the warp must call it.
+struct N2vOut {
+  uint32_t mask;  // bit k: neighbour id k of the quad is adjacent to prev
+  int64_t from;   // where the next block's window starts
+};
+// Not inlined on purpose: it is called from every place that forms a bias, and one copy keeps
+// the kernel inside the instruction cache (with the body inlined everywhere the warps stalled
+// on instruction fetch 25 cycles per issued instruction).
+__device__ __noinline__ N2vOut n2v_linked_impl(const int32_t* __restrict__ adj, int64_t from, int64_t pe,
+                                               uint32_t head, uint32_t tail, int4 nb, uint32_t q, bool boundary,
+                                               uint32_t lane, uint32_t* flags) {
+  // effective ids: edges outside the row become -inf / +inf so the 128 ids stay ascending
+  int32_t x[4] = {nb.x, nb.y, nb.z, nb.w};
+  if (boundary) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t r = 4u * q + k;
+      if (r < head) x[k] = (int32_t)0x80000000;
+      else if (r >= tail) x[k] = 0x7FFFFFFF;
+    }
+  }
+  int32_t lmax = (int32_t)0x80000000;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) lmax = x[k] != 0x7FFFFFFF ? max(lmax, x[k]) : lmax;
+  const int32_t xmax = __reduce_max_sync(0xFFFFFFFFu, lmax);
+  const int64_t wlo = from;
+  bool inb = wlo + lane < pe;
+  int32_t pv = inb ? __ldg(adj + wlo + lane) : 0x7FFFFFFF;
+  uint32_t act = __ballot_sync(0xFFFFFFFFu, inb && pv <= xmax);  // a prefix of ones
+  int64_t whi = wlo + __popc(act);
+  if (act == 0xFFFFFFFFu && xmax != 0x7FFFFFFF) whi = warp_lower_bound(adj, wlo + 32, pe, xmax + 1, lane);
+  uint32_t mine = 0;
+  if (whi - wlo > kN2vStreamMax) {  // warp-uniform
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (x[k] != (int32_t)0x80000000 && x[k] != 0x7FFFFFFF && row_contains(adj, wlo, whi, x[k])) mine |= 1u << k;
+    return N2vOut{mine, whi};
+  }
+  flags[lane] = 0u;
+  __syncwarp();
+  for (int64_t base = wlo;;) {
+    // position of pv among the lanes' first ids: pos = number of lanes whose x[0] <= pv
+    uint32_t pos = 0;
+#pragma unroll
+    for (uint32_t step = 16; step > 0; step >>= 1) {
+      const int32_t v = __shfl_sync(0xFFFFFFFFu, x[0], (int)(pos + step - 1u));
+      pos += v <= pv ? step : 0u;
+    }
+    pos += __shfl_sync(0xFFFFFFFFu, x[0], (int)pos) <= pv ? 1u : 0u;
+    const int src = (int)(pos ? pos - 1u : 0u);
+    const int32_t y0 = __shfl_sync(0xFFFFFFFFu, x[0], src), y1 = __shfl_sync(0xFFFFFFFFu, x[1], src);
+    const int32_t y2 = __shfl_sync(0xFFFFFFFFu, x[2], src), y3 = __shfl_sync(0xFFFFFFFFu, x[3], src);
+    const uint32_t eq = (y0 == pv ? 1u : 0u) | (y1 == pv ? 2u : 0u) | (y2 == pv ? 4u : 0u) | (y3 == pv ? 8u : 0u);
+    if (((act >> lane) & 1u) && pos && eq) atomicOr(&flags[src], eq);
+    base += 32;
+    if (base >= whi) break;  // warp-uniform
+    inb = base + lane < whi;
+    pv = inb ? __ldg(adj + base + lane) : 0x7FFFFFFF;
+    act = __ballot_sync(0xFFFFFFFFu, inb);
+  }
+  __syncwarp();
+  mine = flags[lane];
+  // parallel edges: equal ids are adjacent; a match was flagged on the last lane that starts at
+  // or below the value, so copies earlier in the run inherit it from their successor
+  for (;;) {
+    const int32_t nx0 = __shfl_down_sync(0xFFFFFFFFu, x[0], 1);
+    const uint32_t nf = __shfl_down_sync(0xFFFFFFFFu, mine, 1);
+    uint32_t upd = mine;
+    if (lane < 31u && x[3] == nx0 && (nf & 1u)) upd |= 8u;
+    if (x[2] == x[3] && (upd & 8u)) upd |= 4u;
+    if (x[1] == x[2] && (upd & 4u)) upd |= 2u;
+    if (x[0] == x[1] && (upd & 2u)) upd |= 1u;
+    const bool changed = upd != mine;
+    mine = upd;
+    if (!__any_sync(0xFFFFFFFFu, changed)) break;
+  }
+  return N2vOut{mine, whi};
+}
+
+__device__ __forceinline__ uint32_t n2v_linked(const WalkArgs& a, const StepCtx& c, int4 nb, uint32_t q,
+                                               bool boundary, uint32_t lane, uint32_t* flags) {
+  const N2vOut o = n2v_linked_impl(a.adj, c.from, c.pe, c.head, c.tail, nb, q, boundary, lane, flags);
+  c.from = o.from;
+  return o.mask;
+}
+
 // Biases of the four edges of quad q from its raw 16 bytes (`nb`: the four
-// neighbour ids, node2vec only).  Edges outside the row are NOT masked here.
+// neighbour ids and `linked`, which of them are adjacent to the previous vertex: node2vec
+// only).  Edges outside the row are NOT masked here.
 // CLEAN: the weights are known to be >= 0 and not NaN, so the clamp is skipped.
 template <int APP, bool CLEAN>
-__device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c, int4 raw, int4 nb, uint32_t q) {
+__device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c, int4 raw, int4 nb, uint32_t q,
+                                            uint32_t linked = 0u) {
   float4 v;
   if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
     v.x = raw.x == c.want ? 1.0f : 0.0f;
@@ -145,7 +278,7 @@ __device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c,
         const uint32_t r = 4u * q + k;
         if (r < c.head || r >= c.tail) continue;
         if (xs[k] == c.prev) vs[k] = __fmul_rn(vs[k], a.inv_p);
-        else if (!row_contains(a.adj, c.pb, c.pe, xs[k])) vs[k] = __fmul_rn(vs[k], a.inv_q);
+        else if (!((linked >> k) & 1u)) vs[k] = __fmul_rn(vs[k], a.inv_q);
       }
       v = make_float4(vs[0], vs[1], vs[2], vs[3]);
     }
@@ -178,7 +311,9 @@ __device__ __forceinline__ float4 load_quad(const WalkArgs& a, const StepCtx& c,
   const bool valid = q < c.nq;
   const int4 raw = valid ? __ldg(c.prim + q) : zero;
   const int4 nb = (APP == FW_APP_NODE2VEC && valid) ? __ldg(c.sec + q) : zero;
-  float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q);
+  uint32_t linked = 0u;
+  if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb, q, true, threadIdx.x & 31u, c.flags);
+  float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, linked);
   if (boundary) mask_quad(v, q, c.head, c.tail);
   return v;
 }
@@ -295,8 +430,12 @@ __device__ __forceinline__ bool ring_step(const WalkArgs& a, const StepCtx& c, u
   for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? st[fw::kQuadsPerSuper + lane + 32 * j] : zero;
   float S[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
-    S[j] = sum4(quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], s * fw::kQuadsPerSuper + lane + 32u * j));
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t q = s * fw::kQuadsPerSuper + lane + 32u * j;
+    uint32_t linked = 0u;
+    if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb[j], q, false, lane, c.flags);
+    S[j] = sum4(quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], q, linked));
+  }
   const float W = sum_strip(S);
   // Every lane's W is formed (its staged values are consumed) before the stage is refilled.
   if (!__all_sync(0xFFFFFFFFu, ok && W >= 0.0f)) return false;
@@ -324,10 +463,14 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   const int4 zero = make_int4(0, 0, 0, 0);
   if (MODE == FW_GROUP_EDGE) {
     uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu;
-    for (uint32_t q = lane; q < c.nq; q += 32) {
-      const int4 raw = __ldg(c.prim + q);
-      const int4 nb = APP == FW_APP_NODE2VEC ? __ldg(c.sec + q) : zero;
-      float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q);
+    for (uint32_t base = 0; base < c.nq; base += 32) {  // warp-uniform trip count
+      const uint32_t q = base + lane;
+      const bool valid = q < c.nq;
+      const int4 raw = valid ? __ldg(c.prim + q) : zero;
+      const int4 nb = (APP == FW_APP_NODE2VEC && valid) ? __ldg(c.sec + q) : zero;
+      uint32_t linked = 0u;
+      if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb, q, true, lane, c.flags);
+      float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, linked);
       mask_quad(v, q, c.head, c.tail);
       const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.k0, a.k1);
       const float vs[4] = {v.x, v.y, v.z, v.w};
@@ -416,15 +559,33 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   const uint32_t B = best.id;
   const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u));
   float4 v[4];
-  const float W = strip_global<APP, CLEAN>(a, c, B >> 5, B & 31u, v);
+  float W;
+  if (APP == FW_APP_NODE2VEC) {
+    // the membership test works on whole blocks: sweep the winning supergroup again as a warp
+    // and take the winner lane's strip
+    c.from = c.pb;  // it may lie before the blocks just visited
+    W = strip_global<APP, CLEAN>(a, c, B >> 5, lane, v);
+    const int src = (int)(B & 31u);
+    W = __shfl_sync(0xFFFFFFFFu, W, src);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j].x = __shfl_sync(0xFFFFFFFFu, v[j].x, src);
+      v[j].y = __shfl_sync(0xFFFFFFFFu, v[j].y, src);
+      v[j].z = __shfl_sync(0xFFFFFFFFu, v[j].z, src);
+      v[j].w = __shfl_sync(0xFFFFFFFFu, v[j].w, src);
+    }
+  } else {
+    W = strip_global<APP, CLEAN>(a, c, B >> 5, B & 31u, v);
+  }
   const uint32_t cnt = pick_in_strip(v, __fmul_rn((float)(pick >> 8) * 0x1p-24f, W));
   return 4u * ((B >> 5) * fw::kQuadsPerSuper + (B & 31u) + 32u * (cnt >> 2)) + (cnt & 3u);
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
-__global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_APP_NODE2VEC ? FW_MIN_BLOCKS : 2) walk_kernel(const __grid_constant__ WalkArgs a) {
+__global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_APP_NODE2VEC ? FW_MIN_BLOCKS : (MODE == FW_GROUP_STRIP ? FW_N2V_MIN_BLOCKS : 2)) walk_kernel(const __grid_constant__ WalkArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
+  __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_STRIP ? kStages * stage_bytes<APP>() : 0u;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
@@ -464,7 +625,7 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
       int32_t cur = __ldg(a.starts + qi);
       if (lane == 0) row_out[0] = cur;
       StepCtx c;
-      c.prev = -1; c.pb = 0; c.pe = 0; c.want = 0;
+      c.prev = -1; c.pb = 0; c.pe = 0; c.want = 0; c.from = 0; c.flags = &s_flags[warp][0];
       int k = 0;
       if (cur < 0 || (int64_t)cur >= a.V) {
         status |= FW_STATUS_BAD_START;
@@ -479,6 +640,7 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
           c.head = (uint32_t)(b - 4 * q0);
           c.tail = (uint32_t)(e - 4 * q0);
           if (APP == FW_APP_METAPATH) c.want = a.schema[k % a.schema_len];
+          c.from = c.pb;
           const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, (uint32_t)k, qlo, qhi, lane, ring, ring_ptr);
           if (rel == 0xFFFFFFFFu) break;  // include/walker.cuh:1373-1374 (or a failed wait)
           const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
