@@ -148,29 +148,73 @@ def workload_name(args):
 
 
 def run_reference(args):
-    """Reference arm.  The reference has no CPU implementation of the walk (CUDA only), so
-    this arm times the CPU golden walker -- the OpenMP port of the same semantics -- with all
-    host threads on a bounded seeded sample of the same workload per step."""
+    """Reference arm.  When the reference's own CUDA walker was rebuilt for sm_100
+    (oracle/_ref/ref_walk: its unmodified walk.cu / util.cu / headers behind a harness) and a
+    GPU is present, this times THAT on the same graph and start vertices: `value` from its
+    walk_test path (kernel only, the time the reference itself measures), `e2e` from its
+    walk_batch path (pinned host result, copies inside its timed region).  The reference has
+    no CPU implementation of the walk; `cpu_baseline` is the OpenMP port of the same semantics
+    (the golden walker).  Without the binary or a GPU the port is the value too."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import tempfile
     import flowwalker_artifact_b200 as fw
-    g = fw.rmat(args.scale, args.edge_factor << args.scale, device=0 if _has_cuda() else -1)
-    vals = []
-    info = None
-    for i in range(args.warmup + args.steps):
-        info = cpu_baseline(g, args, budget_s=6.0)
-        if i >= args.warmup:
-            vals.append(info["value"])
-    v = statistics.mean(vals)
-    info["value"] = v
-    line = {"impl": "reference", "metric": "walk steps/sec", "value": v, "unit": "walk steps/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(args), "device": "host CPU"},
-            "cpu_baseline": info,
-            "e2e": {"value": v, "unit": "walk steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    have_gpu = _has_cuda()
+    g = fw.rmat(args.scale, args.edge_factor << args.scale, n_labels=5 if args.app == "metapath" else 0,
+                device=0 if have_gpu else -1)
+    ref_bin = os.path.join(ROOT, "oracle", "_ref", "ref_walk")
+    line = {"impl": "reference", "metric": "walk steps/sec", "unit": "walk steps/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
+    cpu = cpu_baseline(g, args, budget_s=12.0, full=True)
+    done = False
+    if have_gpu and os.path.exists(ref_bin):
+        n = args.queries or g.V
+        with tempfile.TemporaryDirectory() as tmp:
+            prefix = os.path.join(tmp, "g")
+            g.save(prefix)
+            starts = np.arange(n, dtype=np.int32) if n == g.V else \
+                np.random.default_rng(4).integers(0, g.V, n).astype(np.int32)
+            sp = os.path.join(tmp, "starts.bin")
+            starts.tofile(sp)
+            cmd = [ref_bin, prefix, args.app, str(args.d), sp, str(n), "-", "0.2", "2.0", "0.5"]
+            if args.app == "metapath":
+                cmd.append("0,1,2,3,4")
+            out = {}
+            for mode in ("0", "1"):
+                env = dict(os.environ, FW_REF_REPEAT=str(args.warmup + args.steps), FW_REF_BATCH=mode)
+                try:
+                    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+                    recs = [json.loads(ln[8:]) for ln in res.stdout.splitlines() if ln.startswith("REFJSON ")]
+                    if res.returncode == 0 and len(recs) == args.warmup + args.steps:
+                        out[mode] = recs[args.warmup:]
+                    else:
+                        line.setdefault("errors", []).append((res.stdout + res.stderr)[-300:])
+                except Exception as exc:  # noqa: BLE001
+                    line.setdefault("errors", []).append(repr(exc)[:300])
+            if "0" in out:
+                ms = sum(r["ref_ms"] for r in out["0"])
+                st = sum(r["steps"] for r in out["0"])
+                line.update({"value": st / (ms * 1e-3), "ms_per_step": ms / args.steps,
+                             "config": {"workload": workload_name(args), "device": "B200, reference CUDA walker rebuilt for sm_100",
+                                        "queries_per_step": n, "timed": "the reference's own timer around its kernel (walk_test)"}})
+                if "1" in out:
+                    ms1 = sum(r["ref_ms"] for r in out["1"])
+                    st1 = sum(r["steps"] for r in out["1"])
+                    line["e2e"] = {"value": st1 / (ms1 * 1e-3), "unit": "walk steps/s", "h2d_bytes_per_step": 4 * n,
+                                   "d2h_bytes_per_step": 4 * n * (args.d + 1), "ms_per_step": ms1 / args.steps,
+                                   "timed": "the reference's walk_batch timer (copies included)"}
+                else:
+                    line["e2e"] = {"value": line["value"], "unit": "walk steps/s", "h2d_bytes_per_step": 0,
+                                   "d2h_bytes_per_step": 0}
+                done = True
+    if not done:
+        line.update({"value": cpu["value"], "ms_per_step": None,
+                     "config": {"workload": workload_name(args), "device": "host CPU (OpenMP port; reference binary unavailable)"},
+                     "e2e": {"value": cpu["value"], "unit": "walk steps/s", "h2d_bytes_per_step": 0,
+                             "d2h_bytes_per_step": 0}})
+    line["cpu_baseline"] = cpu
     print(json.dumps(line))
 
 
