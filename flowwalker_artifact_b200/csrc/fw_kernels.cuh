@@ -69,11 +69,12 @@ struct StepCtx {
   uint32_t head;     // first valid edge, relative to quad 0
   uint32_t tail;     // one past the last valid edge, relative to quad 0
   int32_t prev;      // previous vertex or -1
-  int64_t pb, pe;    // row of prev (node2vec)
+  const int32_t* prow;  // row of prev (node2vec): prow[0 .. plen)
+  uint32_t plen;
   int32_t want;      // label wanted (MetaPath)
   // node2vec: where in prev's row the next 32-quad block's search starts (blocks of a row
   // are visited in ascending order, rows are sorted)
-  mutable int64_t from;
+  mutable uint32_t from;
   uint32_t* flags;  // 32 words of shared memory owned by this warp
 };
 
@@ -118,141 +119,133 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 
 __device__ __forceinline__ float pos(float x) { return fmaxf(x, 0.0f); }
 
-// include/gpu_graph.cuh:97-118: membership of `target` in a sorted row.
-__device__ __forceinline__ bool row_contains(const int32_t* __restrict__ adj, int64_t lo, int64_t hi,
-                                             int32_t target) {
-  --hi;
-  while (lo <= hi) {
-    const int64_t mid = lo + ((hi - lo) >> 1);
-    const int32_t a = __ldg(adj + mid);
-    if (a == target) return true;
-    if (a < target) lo = mid + 1; else hi = mid - 1;
-  }
-  return false;
-}
-
-// Warp-cooperative lower bound in the sorted range adj[L, R): first index whose value is
+// Warp-cooperative lower bound in the sorted range P[L, R): first index whose value is
 // >= target (R if none).  Each round the 32 lanes probe 32 evenly spaced pivots and one
 // ballot keeps 1/32 of the range, so a row of 10^6 neighbours takes four rounds where the
 // reference's per-thread search (include/gpu_graph.cuh:97-112) takes twenty dependent loads
 // per candidate.  All lanes must call it with the same arguments.
-__device__ __forceinline__ int64_t warp_lower_bound(const int32_t* __restrict__ adj, int64_t L, int64_t R,
-                                                    int32_t target, uint32_t lane) {
-  while (R - L > 32) {
-    const int64_t step = (R - L + 31) >> 5;
-    int64_t idx = L + (int64_t)(lane + 1u) * step - 1;
-    if (idx > R - 1) idx = R - 1;
-    const uint32_t below = __ballot_sync(0xFFFFFFFFu, __ldg(adj + idx) < target);
-    const int cnt = __popc(below);  // pivots are ascending: `below` is a prefix of ones
-    if (cnt == 32) return R;        // the last pivot is adj[R-1]
-    const int64_t nl = L + (int64_t)cnt * step;
-    int64_t nr = nl + step;
-    if (nr > R) nr = R;
-    L = nl;
-    R = nr;
+__device__ __forceinline__ uint32_t warp_lower_bound(const int32_t* __restrict__ P, uint32_t L, uint32_t R,
+                                                     int32_t target, uint32_t lane) {
+  while (R - L > 32u) {
+    const uint32_t step = (R - L + 31u) >> 5;
+    uint32_t idx = L + (lane + 1u) * step - 1u;
+    if (idx > R - 1u) idx = R - 1u;
+    const int cnt = __popc(__ballot_sync(0xFFFFFFFFu, __ldg(P + idx) < target));  // a prefix of ones
+    if (cnt == 32) return R;  // the last pivot is P[R-1]
+    L += (uint32_t)cnt * step;
+    R = min(R, L + step);
   }
-  const int32_t v = L + lane < R ? __ldg(adj + L + lane) : 0x7FFFFFFF;
-  return L + __popc(__ballot_sync(0xFFFFFFFFu, v < target && L + lane < R));
+  const bool inb = L + lane < R;
+  const int32_t v = inb ? __ldg(P + L + lane) : 0x7FFFFFFF;
+  return L + __popc(__ballot_sync(0xFFFFFFFFu, inb && v < target));
 }
 
-constexpr int64_t kN2vStreamMax = 1024;  // windows up to this many entries are streamed, larger ones probed
+constexpr uint32_t kN2vStreamMax = 1024;  // windows up to this many entries are streamed, larger ones probed
 
-// node2vec membership for one 32-quad block: which of this lane's four neighbour ids `nb`
-// (quad q) occur in the previous vertex's sorted row.  Returns a 4-bit mask.
+// node2vec membership for one 32-quad block: which of this lane's four neighbour ids x0..x3
+// occur in the previous vertex's sorted row P[0, plen).  Ids of edges outside the current row
+// must come in as INT_MIN (before its first edge) or INT_MAX (after its last) so that the
+// block's 128 ids are ascending.  Returns the 4-bit mask in the low word and, in the high
+// word, where the next block's search starts.
 //
 // Blocks of a row are visited in ascending order and both rows are sorted, so the part of
-// prev's row that matters starts where the previous block's part ended (c.from) and ends at
+// prev's row that matters starts where the previous block's part ended (`from`) and ends at
 // the first entry above the block's largest id.  That window is streamed 32 entries at a
-// time (one coalesced load per round); every entry looks up its position among the block's
-// 128 ids, which stay in registers, with a binary search by shuffles, and flags a match in
-// shared memory for the lane that holds it.  Cost: about two instructions per window entry
-// and no dependent global loads per candidate, where the reference probes prev's whole row
-// once per candidate (include/gpu_graph.cuh:97-118).  Windows much longer than the block
-// (prev a far bigger hub than the current vertex) fall back to per-candidate probes inside
-// the window, found by the warp-wide search.  Every lane of the warp must call it.
-struct N2vOut {
-  uint32_t mask;  // bit k: neighbour id k of the quad is adjacent to prev
-  int64_t from;   // where the next block's window starts
-};
-// Not inlined on purpose: it is called from every place that forms a bias, and one copy keeps
-// the kernel inside the instruction cache (with the body inlined everywhere the warps stalled
-// on instruction fetch 25 cycles per issued instruction).
-__device__ __noinline__ N2vOut n2v_linked_impl(const int32_t* __restrict__ adj, int64_t from, int64_t pe,
-                                               uint32_t head, uint32_t tail, int4 nb, uint32_t q, bool boundary,
-                                               uint32_t lane, uint32_t* flags) {
-  // effective ids: edges outside the row become -inf / +inf so the 128 ids stay ascending
-  int32_t x[4] = {nb.x, nb.y, nb.z, nb.w};
-  if (boundary) {
+// time (one coalesced load per round); every entry finds its place among the block's 128
+// ids, which stay in registers, by a binary search with shuffles and flags a match in shared
+// memory for the lane that holds it: about two instructions per window entry and no
+// dependent global loads per candidate, where the reference probes prev's whole row once
+// per candidate (include/gpu_graph.cuh:97-118).  Windows much longer than the block (prev
+// a far bigger hub than the current vertex) fall back to per-candidate probes inside the
+// window, found by the warp-wide search.  Every lane of the warp must call it.
+//
+// Not inlined on purpose: it is called from every place that forms a bias, and one copy
+// keeps the kernel inside the instruction cache (with the body inlined everywhere the warps
+// stalled on instruction fetch 25 cycles per issued instruction).
+__device__ __noinline__ unsigned long long n2v_linked_impl(const int32_t* __restrict__ P, uint32_t from,
+                                                           uint32_t plen, int32_t x0, int32_t x1, int32_t x2,
+                                                           int32_t x3, uint32_t lane, uint32_t* flags) {
+  const int32_t kHi = 0x7FFFFFFF, kLo = (int32_t)0x80000000;
+  const int32_t lmax = x3 != kHi ? x3 : x2 != kHi ? x2 : x1 != kHi ? x1 : x0 != kHi ? x0 : kLo;
+  const int32_t xmax = __reduce_max_sync(0xFFFFFFFFu, lmax);
+  bool inb = from + lane < plen;
+  int32_t pv = inb ? __ldg(P + from + lane) : kHi;
+  uint32_t act = __ballot_sync(0xFFFFFFFFu, inb && pv <= xmax);  // a prefix of ones
+  if (act == 0u) return (unsigned long long)from << 32;       // nothing of prev's row in this block's range
+  uint32_t whi = from + (uint32_t)__popc(act);
+  if (act == 0xFFFFFFFFu) whi = warp_lower_bound(P, from + 32u, plen, xmax + 1, lane);
+  uint32_t mine = 0;
+  if (whi - from > kN2vStreamMax) {  // warp-uniform
+    const int32_t xs[4] = {x0, x1, x2, x3};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const uint32_t r = 4u * q + k;
-      if (r < head) x[k] = (int32_t)0x80000000;
-      else if (r >= tail) x[k] = 0x7FFFFFFF;
+      if (xs[k] == kLo || xs[k] == kHi) continue;
+      uint32_t lo = from, hi = whi;
+      while (lo < hi) {
+        const uint32_t mid = lo + ((hi - lo) >> 1);
+        if (__ldg(P + mid) < xs[k]) lo = mid + 1u; else hi = mid;
+      }
+      if (lo < whi && __ldg(P + lo) == xs[k]) mine |= 1u << k;
     }
-  }
-  int32_t lmax = (int32_t)0x80000000;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) lmax = x[k] != 0x7FFFFFFF ? max(lmax, x[k]) : lmax;
-  const int32_t xmax = __reduce_max_sync(0xFFFFFFFFu, lmax);
-  const int64_t wlo = from;
-  bool inb = wlo + lane < pe;
-  int32_t pv = inb ? __ldg(adj + wlo + lane) : 0x7FFFFFFF;
-  uint32_t act = __ballot_sync(0xFFFFFFFFu, inb && pv <= xmax);  // a prefix of ones
-  int64_t whi = wlo + __popc(act);
-  if (act == 0xFFFFFFFFu && xmax != 0x7FFFFFFF) whi = warp_lower_bound(adj, wlo + 32, pe, xmax + 1, lane);
-  uint32_t mine = 0;
-  if (whi - wlo > kN2vStreamMax) {  // warp-uniform
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-      if (x[k] != (int32_t)0x80000000 && x[k] != 0x7FFFFFFF && row_contains(adj, wlo, whi, x[k])) mine |= 1u << k;
-    return N2vOut{mine, whi};
+    return ((unsigned long long)whi << 32) | mine;
   }
   flags[lane] = 0u;
   __syncwarp();
-  for (int64_t base = wlo;;) {
-    // position of pv among the lanes' first ids: pos = number of lanes whose x[0] <= pv
+  for (uint32_t base = from;;) {
+    // pos = number of lanes whose first id is <= pv; the lane before that may hold pv
     uint32_t pos = 0;
 #pragma unroll
     for (uint32_t step = 16; step > 0; step >>= 1) {
-      const int32_t v = __shfl_sync(0xFFFFFFFFu, x[0], (int)(pos + step - 1u));
+      const int32_t v = __shfl_sync(0xFFFFFFFFu, x0, (int)(pos + step - 1u));
       pos += v <= pv ? step : 0u;
     }
-    pos += __shfl_sync(0xFFFFFFFFu, x[0], (int)pos) <= pv ? 1u : 0u;
+    pos += __shfl_sync(0xFFFFFFFFu, x0, (int)pos) <= pv ? 1u : 0u;
     const int src = (int)(pos ? pos - 1u : 0u);
-    const int32_t y0 = __shfl_sync(0xFFFFFFFFu, x[0], src), y1 = __shfl_sync(0xFFFFFFFFu, x[1], src);
-    const int32_t y2 = __shfl_sync(0xFFFFFFFFu, x[2], src), y3 = __shfl_sync(0xFFFFFFFFu, x[3], src);
+    const int32_t y0 = __shfl_sync(0xFFFFFFFFu, x0, src), y1 = __shfl_sync(0xFFFFFFFFu, x1, src);
+    const int32_t y2 = __shfl_sync(0xFFFFFFFFu, x2, src), y3 = __shfl_sync(0xFFFFFFFFu, x3, src);
     const uint32_t eq = (y0 == pv ? 1u : 0u) | (y1 == pv ? 2u : 0u) | (y2 == pv ? 4u : 0u) | (y3 == pv ? 8u : 0u);
     if (((act >> lane) & 1u) && pos && eq) atomicOr(&flags[src], eq);
-    base += 32;
+    base += 32u;
     if (base >= whi) break;  // warp-uniform
     inb = base + lane < whi;
-    pv = inb ? __ldg(adj + base + lane) : 0x7FFFFFFF;
+    pv = inb ? __ldg(P + base + lane) : kHi;
     act = __ballot_sync(0xFFFFFFFFu, inb);
   }
   __syncwarp();
   mine = flags[lane];
-  // parallel edges: equal ids are adjacent; a match was flagged on the last lane that starts at
-  // or below the value, so copies earlier in the run inherit it from their successor
-  for (;;) {
-    const int32_t nx0 = __shfl_down_sync(0xFFFFFFFFu, x[0], 1);
-    const uint32_t nf = __shfl_down_sync(0xFFFFFFFFu, mine, 1);
-    uint32_t upd = mine;
-    if (lane < 31u && x[3] == nx0 && (nf & 1u)) upd |= 8u;
-    if (x[2] == x[3] && (upd & 8u)) upd |= 4u;
-    if (x[1] == x[2] && (upd & 4u)) upd |= 2u;
-    if (x[0] == x[1] && (upd & 2u)) upd |= 1u;
-    const bool changed = upd != mine;
-    mine = upd;
-    if (!__any_sync(0xFFFFFFFFu, changed)) break;
+  // Parallel edges: equal ids are adjacent, and a match was flagged on the last lane that
+  // starts at or below the value, so earlier copies of the run inherit it from their successor.
+  const int32_t nx0 = __shfl_down_sync(0xFFFFFFFFu, x0, 1);
+  const bool dup = x0 == x1 || x1 == x2 || x2 == x3 || (lane < 31u && x3 == nx0);
+  if (__any_sync(0xFFFFFFFFu, dup && x3 != kHi)) {
+    for (;;) {
+      const uint32_t nf = __shfl_down_sync(0xFFFFFFFFu, mine, 1);
+      uint32_t upd = mine;
+      if (lane < 31u && x3 == nx0 && (nf & 1u)) upd |= 8u;
+      if (x2 == x3 && (upd & 8u)) upd |= 4u;
+      if (x1 == x2 && (upd & 4u)) upd |= 2u;
+      if (x0 == x1 && (upd & 2u)) upd |= 1u;
+      const bool changed = upd != mine;
+      mine = upd;
+      if (!__any_sync(0xFFFFFFFFu, changed)) break;
+    }
   }
-  return N2vOut{mine, whi};
+  return ((unsigned long long)whi << 32) | mine;
 }
 
 __device__ __forceinline__ uint32_t n2v_linked(const WalkArgs& a, const StepCtx& c, int4 nb, uint32_t q,
-                                               bool boundary, uint32_t lane, uint32_t* flags) {
-  const N2vOut o = n2v_linked_impl(a.adj, c.from, c.pe, c.head, c.tail, nb, q, boundary, lane, flags);
-  c.from = o.from;
-  return o.mask;
+                                               bool boundary, uint32_t lane) {
+  if (boundary) {  // edges outside the row become -inf / +inf so the 128 ids stay ascending
+    const int32_t kHi = 0x7FFFFFFF, kLo = (int32_t)0x80000000;
+    const uint32_t r = 4u * q;
+    nb.x = r + 0u < c.head ? kLo : r + 0u >= c.tail ? kHi : nb.x;
+    nb.y = r + 1u < c.head ? kLo : r + 1u >= c.tail ? kHi : nb.y;
+    nb.z = r + 2u < c.head ? kLo : r + 2u >= c.tail ? kHi : nb.z;
+    nb.w = r + 3u < c.head ? kLo : r + 3u >= c.tail ? kHi : nb.w;
+  }
+  const unsigned long long o = n2v_linked_impl(c.prow, c.from, c.plen, nb.x, nb.y, nb.z, nb.w, lane, c.flags);
+  c.from = (uint32_t)(o >> 32);
+  return (uint32_t)o;
 }
 
 // Biases of the four edges of quad q from its raw 16 bytes (`nb`: the four
@@ -274,9 +267,7 @@ __device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c,
       const int32_t xs[4] = {nb.x, nb.y, nb.z, nb.w};
       float vs[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint32_t r = 4u * q + k;
-        if (r < c.head || r >= c.tail) continue;
+      for (int k = 0; k < 4; ++k) {  // edges outside the row are zeroed by the caller's mask
         if (xs[k] == c.prev) vs[k] = __fmul_rn(vs[k], a.inv_p);
         else if (!((linked >> k) & 1u)) vs[k] = __fmul_rn(vs[k], a.inv_q);
       }
@@ -312,7 +303,7 @@ __device__ __forceinline__ float4 load_quad(const WalkArgs& a, const StepCtx& c,
   const int4 raw = valid ? __ldg(c.prim + q) : zero;
   const int4 nb = (APP == FW_APP_NODE2VEC && valid) ? __ldg(c.sec + q) : zero;
   uint32_t linked = 0u;
-  if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb, q, true, threadIdx.x & 31u, c.flags);
+  if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb, q, boundary, threadIdx.x & 31u);
   float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, linked);
   if (boundary) mask_quad(v, q, c.head, c.tail);
   return v;
@@ -433,7 +424,7 @@ __device__ __forceinline__ bool ring_step(const WalkArgs& a, const StepCtx& c, u
   for (int j = 0; j < 4; ++j) {
     const uint32_t q = s * fw::kQuadsPerSuper + lane + 32u * j;
     uint32_t linked = 0u;
-    if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb[j], q, false, lane, c.flags);
+    if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb[j], q, false, lane);
     S[j] = sum4(quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], q, linked));
   }
   const float W = sum_strip(S);
@@ -469,7 +460,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
       const int4 raw = valid ? __ldg(c.prim + q) : zero;
       const int4 nb = (APP == FW_APP_NODE2VEC && valid) ? __ldg(c.sec + q) : zero;
       uint32_t linked = 0u;
-      if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb, q, true, lane, c.flags);
+      if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb, q, true, lane);
       float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, linked);
       mask_quad(v, q, c.head, c.tail);
       const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.k0, a.k1);
@@ -563,7 +554,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   if (APP == FW_APP_NODE2VEC) {
     // the membership test works on whole blocks: sweep the winning supergroup again as a warp
     // and take the winner lane's strip
-    c.from = c.pb;  // it may lie before the blocks just visited
+    c.from = 0u;  // it may lie before the blocks just visited
     W = strip_global<APP, CLEAN>(a, c, B >> 5, lane, v);
     const int src = (int)(B & 31u);
     W = __shfl_sync(0xFFFFFFFFu, W, src);
@@ -625,7 +616,7 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
       int32_t cur = __ldg(a.starts + qi);
       if (lane == 0) row_out[0] = cur;
       StepCtx c;
-      c.prev = -1; c.pb = 0; c.pe = 0; c.want = 0; c.from = 0; c.flags = &s_flags[warp][0];
+      c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = &s_flags[warp][0];
       int k = 0;
       if (cur < 0 || (int64_t)cur >= a.V) {
         status |= FW_STATUS_BAD_START;
@@ -640,14 +631,14 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
           c.head = (uint32_t)(b - 4 * q0);
           c.tail = (uint32_t)(e - 4 * q0);
           if (APP == FW_APP_METAPATH) c.want = a.schema[k % a.schema_len];
-          c.from = c.pb;
+          c.from = 0u;
           const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, (uint32_t)k, qlo, qhi, lane, ring, ring_ptr);
           if (rel == 0xFFFFFFFFu) break;  // include/walker.cuh:1373-1374 (or a failed wait)
           const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
           if (nxt < 0 || (int64_t)nxt >= a.V) { status |= FW_STATUS_BAD_NEIGHBOR; break; }
           if (lane == 0) row_out[k + 1] = nxt;  // include/walker.cuh:1380-1381
           my_scanned += (unsigned long long)(e - b);
-          c.prev = cur; c.pb = b; c.pe = e;  // include/gpu_task.cuh:70-77
+          c.prev = cur; c.prow = a.adj + b; c.plen = (uint32_t)(e - b);  // include/gpu_task.cuh:70-77
           cur = nxt;
           ++k;
           if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
