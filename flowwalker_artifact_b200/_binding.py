@@ -56,6 +56,7 @@ def lib():
         L = ctypes.CDLL(path)
         L.fw_last_error.restype = ctypes.c_char_p
         vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32
+        L.fw_device_count.argtypes = [ctypes.POINTER(ctypes.c_int)]
         L.fw_graph_load.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(vp)]
         L.fw_graph_save.argtypes = [vp, ctypes.c_char_p]
         L.fw_graph_from_arrays.argtypes = [i64, i64, vp, ctypes.c_int, vp, vp, vp, ctypes.POINTER(vp)]

@@ -53,8 +53,8 @@ def build(force=False, verbose=False):
         subprocess.run([_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"],
                        check=True, env=env)
     cli_src = os.path.join(CSRC, "fw_cli.cpp")
-    if os.path.exists(cli_src) and (force or _stale(CLI, [cli_src, LIB])):
-        subprocess.run(["g++", "-std=c++17", "-O2", "-Wall", "-Wextra", cli_src, "-o", CLI,
+    if os.path.exists(cli_src) and (force or _stale(CLI, [cli_src, LIB, os.path.join(CSRC, "fw_flags.h")])):
+        subprocess.run(["g++", "-std=c++17", "-O2", "-Wall", "-Wextra", "-pthread", cli_src, "-o", CLI,
                         "-L" + HERE, "-lflowwalker", "-Wl,-rpath,$ORIGIN"], check=True, env=env)
     return LIB
 

@@ -173,6 +173,16 @@ int ensure_cap(T** buf, size_t* cap, size_t need) {
 
 }  // namespace
 
+extern "C" int fw_device_count(int* count) {
+  fw::clear_error();
+  if (!count) return fw::fail(FW_ERR_ARG, "fw_device_count: null argument");
+  *count = 0;
+  cudaError_t err = cudaGetDeviceCount(count);
+  if (err == cudaErrorNoDevice || err == cudaErrorInsufficientDriver) { *count = 0; return FW_OK; }
+  if (err != cudaSuccess) return fw::fail(FW_ERR_CUDA, "cudaGetDeviceCount failed: %s", cudaGetErrorString(err));
+  return FW_OK;
+}
+
 extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_engine** out) {
   fw::clear_error();
   if (!g || !out) return fw::fail(FW_ERR_ARG, "fw_engine_create: null argument");

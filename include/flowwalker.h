@@ -93,6 +93,8 @@ typedef struct fw_rmat_params {
 } fw_rmat_params;
 
 const char* fw_last_error(void);
+/* Number of CUDA devices visible to the process. */
+int fw_device_count(int* count);
 
 /* ---- graph: on-disk format of include/graph.cuh:93-190, writer data/EdgeListToCSR.cpp:217-251 ---- */
 

@@ -1,0 +1,87 @@
+"""The flowwalker command line: the reference's flags (src/main.cu:40-80), its flag rewriting
+and result consumers, on top of the C ABI."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import flowwalker_artifact_b200 as fw
+import graphs
+import oracle_lib as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CLI = os.path.join(ROOT, "flowwalker_artifact_b200", "flowwalker")
+
+
+def run(*args, **kw):
+    return subprocess.run([CLI] + list(args), capture_output=True, text=True, timeout=600, **kw)
+
+
+def test_flag_errors_and_help():
+    assert os.path.exists(CLI), "build the CLI with python -m flowwalker_artifact_b200.build"
+    r = run("--help")
+    assert r.returncode == 0
+    for flag in ("--input", "--n", "--all", "--d", "--deepwalk", "--ppr", "--node2vec", "--metapath", "--tp",
+                 "--p", "--q", "--schema", "--batchsize", "--autobatch", "--headroom", "--printresult",
+                 "--printworkload", "--save_degree", "--b_file", "--walkmode", "--dprs", "--syn", "--lognorm"):
+        assert flag + " " in r.stdout, flag
+    assert run("--bogus").returncode == 2
+    assert run("--n", "abc").returncode == 2
+    assert run("--n").returncode == 2
+    r = run("--input", "/nonexistent/prefix", "--deepwalk")
+    assert r.returncode == 1 and "cannot open" in r.stderr
+
+
+def test_needs_exactly_one_app(tmp_path):
+    g = graphs.config1()
+    prefix = str(tmp_path / "g")
+    g.save(prefix)
+    r = run("--input", prefix)
+    assert r.returncode == 0 and "Please choose a walk mode" in r.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("app,flags,kw", [
+    (fw.APP_DEEPWALK, ["--deepwalk", "--d=20"], dict(d=20)),
+    (fw.APP_NODE2VEC, ["--node2vec", "--d", "20", "--p=0.5", "--q", "2"], dict(d=20, p=0.5, q=2.0)),
+    (fw.APP_METAPATH, ["--metapath", "--schema=1,2,3"], dict(d=3, schema=[1, 2, 3])),
+])
+def test_cli_walks_match_the_golden_walker(tmp_path, app, flags, kw):
+    g = graphs.config1()
+    prefix = str(tmp_path / "g")
+    g.save(prefix)
+    out = str(tmp_path / "walks.bin")
+    bucket = str(tmp_path / "bucket.csv")
+    r = run("--input", prefix, "--all", "--printworkload", "--save_degree", "--b_file", bucket,
+            "--save_result", out, "--seed=77", *flags)
+    assert r.returncode == 0, r.stdout + r.stderr
+    walks = np.fromfile(out, dtype=np.int32).reshape(g.V, kw["d"] + 1)
+    ref, steps, scanned, _ = O.graph_walk(g, app, np.arange(g.V, dtype=np.int32), seed=77, **kw)
+    assert (walks == ref).all()
+    assert "Total sampled vertex: %d" % steps in r.stdout
+    assert "Total sampled edge: %d" % scanned in r.stdout
+    summary = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+    assert summary["steps"] == steps and summary["scanned"] == scanned and summary["device_status"] == 0
+    rows = [ln.split(",") for ln in open(bucket).read().split()]
+    assert sum(int(c) for _, c in rows) == steps
+
+
+@pytest.mark.gpu
+def test_cli_batches_and_printresult(tmp_path):
+    g = graphs.config1()
+    prefix = str(tmp_path / "g")
+    g.save(prefix)
+    out = str(tmp_path / "walks.bin")
+    r = run("--input", prefix, "--ppr", "--n", "1000", "--uniformstarts", "--startseed=9", "--batch",
+            "--batchsize", "300", "--printresult", "--save_result", out)
+    assert r.returncode == 0, r.stdout + r.stderr
+    walks = np.fromfile(out, dtype=np.int32).reshape(1000, 81)
+    ref = O.graph_walk(g, fw.APP_PPR, walks[:, 0].copy(), d=80, tp=0.2)[0]
+    assert (walks == ref).all()
+    assert r.stdout.count("Walker ") == 100 and "Total length=" in r.stdout
+    # reference default for PPR: every query starts at the vertex of largest out-degree
+    r = run("--input", prefix, "--ppr", "--n", "50", "--save_result", out)
+    assert r.returncode == 0
+    assert (np.fromfile(out, dtype=np.int32).reshape(50, 81)[:, 0] == g.max_degree()[0]).all()
