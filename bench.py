@@ -105,6 +105,13 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+# DRAM bytes per algorithmic byte of the DeepWalk config-2 launch, from the ncu capture summarised
+# in profiles/walk_kernel_deepwalk_scale22_tma_ring.md (dram__bytes_read.sum + write.sum = 52.97 GB
+# for 249.05 GB algorithmic on a 1,000,000-query launch of the same graph; both grow in proportion
+# with the number of queries).  Only valid for that workload: other runs report traffic = null.
+DRAM_PER_ALGORITHMIC_BYTE = 0.2127
+
+
 def algorithmic_bytes(app, scanned, steps, n, xadj_bits):
     """Weights (or labels) read once per scanned neighbour, plus per step the chosen
     neighbour id, the two row bounds of the new vertex and the result cell, plus per
@@ -339,7 +346,11 @@ def main():
             "gpu_launches": dev["launches"],
             "clocks": dev["clocks"],
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_kind + " copy bandwidth",
+                         "frac": achieved / peak,
+                         "traffic": (DRAM_PER_ALGORITHMIC_BYTE * per_launch_bytes
+                                     if (args.app, args.scale, args.edge_factor, args.d) == ("deepwalk", 22, 16, 80) else None),
+                         "traffic_source": "ncu dram bytes of a 1,000,000-query launch scaled by algorithmic bytes",
+                         "peak_source": peak_kind + " copy bandwidth",
                          "kernel": "walk_kernel", "algorithmic_bytes_per_launch": per_launch_bytes,
                          "kernel_ms_per_launch": per_launch_ms},
         }
