@@ -40,7 +40,7 @@ def parse():
     ap.add_argument("--scale", type=int, default=22)
     ap.add_argument("--edge-factor", type=int, default=16)
     ap.add_argument("--d", type=int, default=80)
-    ap.add_argument("--group", type=int, default=0, help="sampler granularity: 0 default, 1 or 16")
+    ap.add_argument("--group", type=int, default=0, help="sampler granularity: 0 default, 1 or 64")
     ap.add_argument("--queries", type=int, default=0, help="0 = all vertices")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -129,7 +129,7 @@ def cpu_baseline(g, args, budget_s=12.0, full=False):
     V = g.V
     rng = np.random.default_rng(4)
     app = APPS[args.app]
-    kw = dict(d=args.d, group_mode=args.group or 16)
+    kw = dict(d=args.d, group_mode=args.group or 64)
     if args.app == "metapath":
         kw["schema"] = [0, 1, 2, 3, 4]
     cores = O.lib().fwo_max_threads()
@@ -340,7 +340,7 @@ def main():
             "config": {"workload": workload_name(args), "queries_per_gpu_per_step": n,
                        "vertices": V, "edges": g.E, "walk_steps_per_pass": dev["steps"] // (args.steps * world),
                        "scanned_per_pass": dev["scanned"] // (args.steps * world),
-                       "group_mode": args.group or 16, "parallelism": "queries sharded, graph replicated x%d" % world,
+                       "group_mode": args.group or 64, "parallelism": "queries sharded, graph replicated x%d" % world,
                        "l2": "inputs larger than L2 (weights %.0f MB, results %.0f MB per pass)" % (
                            4 * g.E / 1e6, 4 * n * D / 1e6)},
             "gpu_launches": dev["launches"],

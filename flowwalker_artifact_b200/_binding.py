@@ -6,7 +6,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
 APP_DEEPWALK, APP_PPR, APP_NODE2VEC, APP_METAPATH = 0, 1, 2, 3
-GROUP_EDGE, GROUP_STRIP = 1, 16
+GROUP_EDGE, GROUP_STRIP = 1, 64
 
 
 class FlowWalkerError(RuntimeError):

@@ -53,7 +53,7 @@ void define_flags(fwflags::Parser& fl) {
   fl.add("seed", Flag::kInt, "1337", "walk seed (Philox key)");
   fl.add("startseed", Flag::kInt, "4", "seed of the random start points (the reference uses time(NULL))");
   fl.add("uniformstarts", Flag::kBool, "false", "ppr: seeded uniform start points instead of the max-degree vertex");
-  fl.add("group", Flag::kInt, "0", "sampler granularity: 0 default, 1 per neighbour, 16 per strip");
+  fl.add("group", Flag::kInt, "0", "sampler granularity: 0 default, 1 per neighbour, 64 per strip");
   fl.add("gpus", Flag::kInt, "1", "number of GPUs: queries are sharded, the graph is replicated");
   fl.add("save_result", Flag::kString, "", "write the int32 [n x (d+1)] walk table to this file");
 }

@@ -2,10 +2,10 @@
 //
 // One persistent grid; every warp claims queries from a global atomic counter
 // and walks them to completion.  Per step the row of the current vertex is
-// swept in 2 KB supergroups with aligned 128-bit accesses:
+// swept in 2 KB sub-blocks with aligned 128-bit accesses:
 //   * short rows: straight from global memory (four independent loads per lane);
 //   * long rows : through a per-warp ring in shared memory filled by TMA bulk
-//                 copies (cp.async.bulk + mbarrier), so the next supergroups are
+//                 copies (cp.async.bulk + mbarrier), so the next sub-blocks are
 //                 in flight while the current one is reduced.
 // Stands in for include/walker.cuh:1307-1580, include/sampler.cuh:46-200,
 // include/app.cuh:58-152, include/gpu_task.cuh:24-78 and include/myrand.cuh
@@ -34,8 +34,7 @@ constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared
 #define FW_MIN_BLOCKS 5
 #endif
 constexpr int kStages = FW_STAGES;       // ring depth per warp
-constexpr uint32_t kSuperBytes = 16u * fw::kQuadsPerSuper;  // 2 KB
-constexpr uint32_t kRingMinSuper = 3;    // rows with at least this many supergroups use the ring
+constexpr uint32_t kSubBytes = 16u * fw::kQuadsPerSub;  // 2 KB: one ring stage, one bulk copy
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls of an mbarrier before giving up
 
 // Scratch words (uint64) in device memory.
@@ -309,19 +308,18 @@ __device__ __forceinline__ float4 load_quad(const WalkArgs& a, const StepCtx& c,
   return v;
 }
 
-// Lane `lane`'s strip of supergroup s from global memory: total bias, the four
-// quads optionally kept.  Blocks past the end of the row are skipped as a warp.
+// Lane `lane`'s four quads of sub-block b (quads 128 b + 32 j + lane, j = 0..3) from global
+// memory: their total bias in the fixed order (S0+S1)+(S2+S3).  Blocks of 32 quads past the
+// end of the row are skipped as a warp.
 template <int APP, bool CLEAN>
-__device__ __forceinline__ float strip_global(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t lane,
-                                              float4* keep) {
+__device__ __forceinline__ float sub_global(const WalkArgs& a, const StepCtx& c, uint32_t b, uint32_t lane) {
   const uint32_t last_blk = (c.nq - 1u) >> 5;
   float S[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const uint32_t blk = 4u * s + j;
+    const uint32_t blk = 4u * b + j;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (blk <= last_blk) v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, blk == 0u || blk == last_blk);
-    if (keep) keep[j] = v;
     S[j] = sum4(v);
   }
   return sum_strip(S);
@@ -334,16 +332,18 @@ __device__ __forceinline__ void warp_argmin(uint32_t& key, uint32_t& id) {
   key = m;
 }
 
-// A lane's best candidate so far.
+// A lane's best candidate so far: key bits, strip id, the pick word of its Philox block and
+// the strip's total bias.
 struct Best {
   uint32_t key, id, pick;
+  float W;
 };
 
 // Exact test of one strip: key = E(x) / W.
 __device__ __forceinline__ void offer(Best& b, uint32_t x, uint32_t pick_word, float W, uint32_t id) {
   if (W > 0.0f) {
     const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(x), W));
-    if (bits < b.key) { b.key = bits; b.id = id; b.pick = pick_word; }
+    if (bits < b.key) { b.key = bits; b.id = id; b.pick = pick_word; b.W = W; }
   }
 }
 
@@ -369,44 +369,26 @@ struct Ring {
 
 template <int APP>
 __device__ __forceinline__ constexpr uint32_t stage_bytes() {
-  return APP == FW_APP_NODE2VEC ? 2u * kSuperBytes : kSuperBytes;
+  return APP == FW_APP_NODE2VEC ? 2u * kSubBytes : kSubBytes;
 }
 
-// Inverse-CDF pick among the 16 biases of a strip in canonical order (quad j, edge k):
-// the first edge whose running sum exceeds thr.  Zero biases leave the running sum
-// unchanged, so the count of sums <= thr is that edge's position; 16 means rounding
-// pushed thr past the sequential total, and the last positive edge is taken.
-__device__ __forceinline__ uint32_t pick_in_strip(const float4 v[4], float thr) {
-  float acc = 0.0f;
-  uint32_t cnt = 0;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      acc = __fadd_rn(acc, vs[k]);
-      cnt += acc <= thr ? 1u : 0u;
-    }
-  }
-  if (cnt >= 16u) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float vs[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (vs[k] > 0.0f) cnt = 4u * j + k;
-    }
-  }
-  return cnt;
+// Issues the bulk copies of sub-block b into stage T (lane 0 only calls this).
+template <int APP>
+__device__ __forceinline__ void ring_fill(const StepCtx& c, const Ring& ring, uint32_t b, uint32_t T) {
+  constexpr uint32_t kSB = stage_bytes<APP>();
+  const uint32_t bar = ring.bar + 8u * T;
+  mbar_expect_tx(bar, kSB);
+  bulk_g2s(ring.data + T * kSB, c.prim + (size_t)b * fw::kQuadsPerSub, kSubBytes, bar);
+  if (APP == FW_APP_NODE2VEC) bulk_g2s(ring.data + T * kSB + kSubBytes, c.sec + (size_t)b * fw::kQuadsPerSub, kSubBytes, bar);
 }
 
-// One interior supergroup s from stage T of the ring: wait for its copy, reduce the lane's
-// strip, hand the stage back (refill with supergroup s + kStages), then test the strip's key
-// (random word x, pick word pw).  False when the wait ran out.
+// One interior sub-block b from stage T of the ring: wait for its copy, reduce the lane's
+// four quads into A, hand the stage back (refill with sub-block b + kStages, while it is
+// still interior).  False when the wait ran out.
 template <int APP, bool CLEAN>
-__device__ __forceinline__ bool ring_step(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t last,
-                                          uint32_t lane, Ring& ring, const unsigned char* ring_ptr, uint32_t x,
-                                          uint32_t pw, Best& best, const uint32_t T) {
+__device__ __forceinline__ bool ring_sub(const WalkArgs& a, const StepCtx& c, uint32_t b, uint32_t last_b,
+                                         uint32_t lane, Ring& ring, const unsigned char* ring_ptr, const uint32_t T,
+                                         float& A) {
   constexpr uint32_t kSB = stage_bytes<APP>();
   const uint32_t bar = ring.bar + 8u * T;
   bool ok = mbar_try_wait(bar, (ring.parity >> T) & 1u) != 0;
@@ -418,28 +400,19 @@ __device__ __forceinline__ bool ring_step(const WalkArgs& a, const StepCtx& c, u
 #pragma unroll
   for (int j = 0; j < 4; ++j) raw[j] = st[lane + 32 * j];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? st[fw::kQuadsPerSuper + lane + 32 * j] : zero;
+  for (int j = 0; j < 4; ++j) nb[j] = APP == FW_APP_NODE2VEC ? st[fw::kQuadsPerSub + lane + 32 * j] : zero;
   float S[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const uint32_t q = s * fw::kQuadsPerSuper + lane + 32u * j;
+    const uint32_t q = b * fw::kQuadsPerSub + lane + 32u * j;
     uint32_t linked = 0u;
     if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb[j], q, false, lane);
     S[j] = sum4(quad_bias<APP, CLEAN>(a, c, raw[j], nb[j], q, linked));
   }
-  const float W = sum_strip(S);
-  // Every lane's W is formed (its staged values are consumed) before the stage is refilled.
-  if (!__all_sync(0xFFFFFFFFu, ok && W >= 0.0f)) return false;
-  if (lane == 0 && s + kStages < last) {
-    mbar_expect_tx(bar, kSB);
-    bulk_g2s(ring.data + T * kSB, c.prim + (size_t)(s + kStages) * fw::kQuadsPerSuper, kSuperBytes, bar);
-    if (APP == FW_APP_NODE2VEC)
-      bulk_g2s(ring.data + T * kSB + kSuperBytes, c.sec + (size_t)(s + kStages) * fw::kQuadsPerSuper, kSuperBytes,
-               bar);
-  }
-  // the warp-wide best so far bounds every lane's candidates
-  const float bound = __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key));
-  offer_filtered(best, x, pw, W, s * 32u + lane, bound);
+  A = sum_strip(S);
+  // Every lane's A is formed (its staged values are consumed) before the stage is refilled.
+  if (!__all_sync(0xFFFFFFFFu, ok && A >= 0.0f)) return false;
+  if (lane == 0 && b + kStages < last_b) ring_fill<APP>(c, ring, b + kStages, T);
   return true;
 }
 
@@ -479,9 +452,10 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   }
 
   // ---- strips ----
-  // Philox block g of lane l (counter word 0 = g*32 + l) serves supergroups 3g, 3g+1, 3g+2
-  // (words 0..2 -> keys) and carries in word 3 the uniform for the in-strip pick.
-  Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u};
+  // Strip (s,l): the 16 quads 512 s + 32 j + l.  Philox block g of lane l (counter word
+  // 0 = g*32 + l) serves supergroups 3g, 3g+1, 3g+2 (words 0..2 -> keys) and carries in
+  // word 3 the uniform for the in-strip pick.
+  Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
   fw::Philox4 r = fw::philox4x32_10(lane, c1, qlo, qhi, a.k0, a.k1);
 
   if (c.nq <= 32u) {
@@ -503,73 +477,115 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     return 4u * (uint32_t)src + cnt;
   }
 
-  const uint32_t nsuper = (c.nq + fw::kQuadsPerSuper - 1) / fw::kQuadsPerSuper;
-  if (nsuper < kRingMinSuper) {  // at most two supergroups: block 0 covers them
-    offer(best, r.x, r.w, strip_global<APP, CLEAN>(a, c, 0, lane, nullptr), lane);
-    if (nsuper > 1) offer(best, r.y, r.w, strip_global<APP, CLEAN>(a, c, 1, lane, nullptr), 32u + lane);
-  } else {
-    // first and last supergroups straight from global memory (boundary quads, partial fill);
-    // the interior ones [1, last) through the ring
-    const uint32_t last = nsuper - 1;
-    constexpr uint32_t kSB = stage_bytes<APP>();
-    if (lane == 0) {
+  // The row is swept in sub-blocks of 128 quads (2 KB): the first and the last straight from
+  // global memory (boundary quads, partial fill), the interior ones through the ring when
+  // there are any.  Four sub-blocks make a supergroup; a lane's four partial sums A0..A3 are
+  // combined as (A0+A1)+(A2+A3) and tested once per supergroup.
+  const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
+  const uint32_t last_b = nb - 1u;
+  if (nb >= 3u && lane == 0) {
 #pragma unroll
-      for (uint32_t t = 0; t < kStages; ++t) {
-        const uint32_t s = 1u + t;
-        if (s < last) {
-          const uint32_t bar = ring.bar + 8u * t;
-          mbar_expect_tx(bar, kSB);
-          bulk_g2s(ring.data + t * kSB, c.prim + (size_t)s * fw::kQuadsPerSuper, kSuperBytes, bar);
-          if (APP == FW_APP_NODE2VEC)
-            bulk_g2s(ring.data + t * kSB + kSuperBytes, c.sec + (size_t)s * fw::kQuadsPerSuper, kSuperBytes, bar);
-        }
+    for (uint32_t t = 0; t < kStages; ++t)
+      if (1u + t < last_b) ring_fill<APP>(c, ring, 1u + t, t);
+  }
+  uint32_t g = 0, m = 0;  // Philox block of the current supergroup, supergroup index mod 3
+  float p01 = 0.0f, a2 = 0.0f;
+  // Adds sub-block b's partial sum; at the end of a supergroup (or of the row) tests its key.
+  auto absorb = [&](float A, uint32_t b, bool row_end, bool filtered) {
+    const uint32_t u = b & 3u;
+    if (u == 0u) p01 = A;
+    else if (u == 1u) p01 = __fadd_rn(p01, A);
+    else if (u == 2u) a2 = A;
+    if (u == 3u || row_end) {
+      const float W = u == 3u ? __fadd_rn(p01, __fadd_rn(a2, A)) : u == 2u ? __fadd_rn(p01, a2) : p01;
+      const uint32_t x = m == 0u ? r.x : m == 1u ? r.y : r.z;
+      const uint32_t id = (b >> 2) * 32u + lane;
+      if (filtered) offer_filtered(best, x, r.w, W, id, __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key)));
+      else offer(best, x, r.w, W, id);
+      if (!row_end) {
+        if (++m == 3u) { m = 0u; r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
       }
     }
-    offer(best, r.x, r.w, strip_global<APP, CLEAN>(a, c, 0, lane, nullptr), lane);
-    uint32_t g = 0, t = 0, m = 1;  // Philox block, ring stage, s mod 3
+  };
+  absorb(sub_global<APP, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false);
+  if (nb >= 3u) {
+    uint32_t t = 0;
     // Kept rolled on purpose: an unrolled sweep measured slower (instruction cache shared by
     // 40 warps that sit at different places of the kernel).
 #pragma unroll 1
-    for (uint32_t s = 1; s < last; ++s) {
-      if (m == 0) r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
-      if (!ring_step<APP, CLEAN>(a, c, s, last, lane, ring, ring_ptr, m == 0 ? r.x : m == 1 ? r.y : r.z, r.w,
-                                 best, t)) {
+    for (uint32_t b = 1; b < last_b; ++b) {
+      float A;
+      if (!ring_sub<APP, CLEAN>(a, c, b, last_b, lane, ring, ring_ptr, t, A)) {
         ring.failed = true;
         return 0xFFFFFFFFu;
       }
+      absorb(A, b, false, true);
       t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
-      m = m == 2u ? 0u : m + 1u;
     }
-    if (m == 0) r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
-    offer(best, m == 0 ? r.x : m == 1 ? r.y : r.z, r.w, strip_global<APP, CLEAN>(a, c, last, lane, nullptr),
-          last * 32u + lane);
   }
+  if (nb > 1u) absorb(sub_global<APP, CLEAN>(a, c, last_b, lane), last_b, true, false);
   warp_argmin(best.key, best.id);
   if (best.id == 0xFFFFFFFFu) return best.id;
-  // pick inside the winning strip B (every lane computes the same)
-  const uint32_t B = best.id;
-  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u));
-  float4 v[4];
-  float W;
-  if (APP == FW_APP_NODE2VEC) {
-    // the membership test works on whole blocks: sweep the winning supergroup again as a warp
-    // and take the winner lane's strip
-    c.from = 0u;  // it may lie before the blocks just visited
-    W = strip_global<APP, CLEAN>(a, c, B >> 5, lane, v);
-    const int src = (int)(B & 31u);
-    W = __shfl_sync(0xFFFFFFFFu, W, src);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      v[j].x = __shfl_sync(0xFFFFFFFFu, v[j].x, src);
-      v[j].y = __shfl_sync(0xFFFFFFFFu, v[j].y, src);
-      v[j].z = __shfl_sync(0xFFFFFFFFu, v[j].z, src);
-      v[j].w = __shfl_sync(0xFFFFFFFFu, v[j].w, src);
+
+  // Inverse-CDF pick inside the winning strip B (every lane computes the same): the first of
+  // its edges in canonical order (quad j, edge k) whose running sum exceeds u * W.  Zero biases
+  // leave the running sum unchanged, so counting the sums <= u * W gives that edge's position.
+  const uint32_t B = best.id, sB = B >> 5, lB = B & 31u;
+  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)lB);
+  const float W = __shfl_sync(0xFFFFFFFFu, best.W, (int)lB);
+  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
+  const uint32_t last_blk = (c.nq - 1u) >> 5;
+  const uint32_t blk0 = 16u * sB;
+  const uint32_t nblk = min(16u, last_blk - blk0 + 1u);
+  if (APP == FW_APP_NODE2VEC) c.from = 0u;  // the strip may lie before the blocks just visited
+  float acc = 0.0f;
+  uint32_t cnt = 0, j = 0;
+#pragma unroll 1
+  for (; j < nblk; ++j) {
+    const uint32_t blk = blk0 + j;
+    const bool edge_blk = blk == 0u || blk == last_blk;
+    float4 v;
+    if (APP == FW_APP_NODE2VEC) {
+      // the membership test works on whole blocks: load the block as a warp, take lane lB's quad
+      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
+      v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
+      v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
+      v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
+      v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
+    } else {
+      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
     }
-  } else {
-    W = strip_global<APP, CLEAN>(a, c, B >> 5, B & 31u, v);
+    acc = __fadd_rn(acc, v.x); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, v.y); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, v.z); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, v.w); cnt += acc <= thr ? 1u : 0u;
+    if (cnt < 4u * (j + 1u)) break;  // found (warp-uniform)
   }
-  const uint32_t cnt = pick_in_strip(v, __fmul_rn((float)(pick >> 8) * 0x1p-24f, W));
-  return 4u * ((B >> 5) * fw::kQuadsPerSuper + (B & 31u) + 32u * (cnt >> 2)) + (cnt & 3u);
+  if (j == nblk) {
+    // rounding pushed u * W past the sequential total: take the strip's last positive edge
+    if (APP == FW_APP_NODE2VEC) c.from = 0u;
+    cnt = 0;
+#pragma unroll 1
+    for (j = 0; j < nblk; ++j) {
+      const uint32_t blk = blk0 + j;
+      const bool edge_blk = blk == 0u || blk == last_blk;
+      float4 v;
+      if (APP == FW_APP_NODE2VEC) {
+        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
+        v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
+        v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
+        v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
+        v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
+      } else {
+        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
+      }
+      if (v.x > 0.0f) cnt = 4u * j;
+      if (v.y > 0.0f) cnt = 4u * j + 1u;
+      if (v.z > 0.0f) cnt = 4u * j + 2u;
+      if (v.w > 0.0f) cnt = 4u * j + 3u;
+    }
+  }
+  return 4u * (32u * (blk0 + (cnt >> 2)) + lB) + (cnt & 3u);
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
@@ -704,7 +720,7 @@ inline KernelFn pick_kernel(int app, int mode, bool clean, int xadj_bits) {
 inline size_t kernel_smem_bytes(int app, int mode, int d, bool hist_in_smem) {
   size_t ring = 0;
   if (mode != FW_GROUP_EDGE)
-    ring = (size_t)kWarpsPerCta * kStages * (app == FW_APP_NODE2VEC ? 2u * kSuperBytes : kSuperBytes);
+    ring = (size_t)kWarpsPerCta * kStages * (app == FW_APP_NODE2VEC ? 2u * kSubBytes : kSubBytes);
   return ring + (hist_in_smem ? (size_t)(d + 1) * 4 : 0);
 }
 

@@ -19,14 +19,19 @@ constexpr uint32_t kPurposeScan = 0u;  // keys of the row scan
 constexpr uint32_t kPurposeStop = 1u;  // PPR stop test after a step
 
 // A row [b,e) of the CSR is addressed in aligned quads of 4 edges (16 bytes):
-// quad q covers absolute edges 4*(q0+q) .. +3 with q0 = b>>2.  A supergroup
-// is 128 consecutive quads (2 KB); strip (s,l) holds quads s*128 + j*32 + l,
-// j = 0..3 -- the four 16-byte loads of lane l when a warp sweeps supergroup s.
+// quad q covers absolute edges 4*(q0+q) .. +3 with q0 = b>>2.  A sub-block is
+// 128 consecutive quads (2 KB, what a warp loads with four 16-byte accesses per
+// lane); a supergroup is four sub-blocks (512 quads, 8 KB).  Strip (s,l) holds
+// the 16 quads s*512 + j*32 + l, j = 0..15 -- everything lane l touches when a
+// warp sweeps supergroup s.  Its total bias is summed in a fixed order: per
+// quad (w0+w1)+(w2+w3), per sub-block (S0+S1)+(S2+S3), then (A0+A1)+(A2+A3).
 // Strip (s,l) has id B = s*32 + l; its key uses word s%3 of the scan block
 // with counter word 0 = (s/3)*32 + l (one Philox block serves three
 // supergroups of a lane); word 3 of that block is the uniform for the pick
 // inside the winning strip.
-constexpr int kQuadsPerSuper = 128;
+constexpr int kQuadsPerSub = 128;
+constexpr int kSubsPerSuper = 4;
+constexpr int kQuadsPerSuper = kQuadsPerSub * kSubsPerSuper;
 
 struct Philox4 { uint32_t x, y, z, w; };
 

@@ -38,7 +38,7 @@ extern "C" {
 
 /* Sampler granularity: how many neighbours share one exponential key. */
 #define FW_GROUP_EDGE 1    /* one key per neighbour */
-#define FW_GROUP_STRIP 16  /* one key per strip of up to 16 neighbours (default) */
+#define FW_GROUP_STRIP 64  /* one key per strip of up to 64 neighbours (default) */
 
 /* Bits of fw_walk_stats.device_status (0 = clean run). */
 #define FW_STATUS_BAD_START 1u     /* a start vertex outside [0,V) (walk has 0 steps) */

@@ -26,8 +26,8 @@
  * every candidate group gets key = E / W, E ~ Exp (in log2 units) drawn from a
  * counter-based Philox stream keyed by (seed; query id, step, group index),
  * W = total bias of the group; the smallest (key, group index) wins.  Group
- * mode 1: one neighbour per group.  Group mode 16: a "strip" of up to 16
- * neighbours (four 16-byte quads 512 bytes apart); the neighbour inside the
+ * mode 1: one neighbour per group.  Group mode 64: a "strip" of up to 64
+ * neighbours (sixteen 16-byte quads 512 bytes apart); the neighbour inside the
  * winning strip is then drawn by inverse CDF with the fourth word of the
  * strip's Philox block (words 0..2 are the keys of three strips).
  *
@@ -154,6 +154,29 @@ static float bias_of(const fwo_ctx* c, int64_t i, int k, int32_t prev) {
   return (b > 0.0f) ? b : 0.0f;
 }
 
+/* Biases (w64, canonical order: quad j, edge cc) and edge indices of strip (s,l) of the row
+ * [b,e): its 16 quads are s*512 + j*32 + l.  Returns the strip's total bias, summed in the
+ * fixed order ((S0+S1)+(S2+S3)) per group of four quads, then (A0+A1)+(A2+A3). */
+static float strip_fill(const fwo_ctx* c, int64_t b, int64_t e, int64_t q0, int64_t nq, int64_t s, int l,
+                        int k, int32_t prev, float* w64, int64_t* i64) {
+  float A[4];
+  for (int g4 = 0; g4 < 4; ++g4) {
+    float S[4];
+    for (int jj = 0; jj < 4; ++jj) {
+      int j = 4 * g4 + jj;
+      int64_t q = s * 512 + j * 32 + l;
+      for (int cc = 0; cc < 4; ++cc) {
+        int64_t i = 4 * (q0 + q) + cc;
+        i64[4 * j + cc] = i;
+        w64[4 * j + cc] = (q < nq && i >= b && i < e) ? bias_of(c, i, k, prev) : 0.f;
+      }
+      S[jj] = (w64[4 * j] + w64[4 * j + 1]) + (w64[4 * j + 2] + w64[4 * j + 3]);
+    }
+    A[g4] = (S[0] + S[1]) + (S[2] + S[3]);
+  }
+  return (A[0] + A[1]) + (A[2] + A[3]);
+}
+
 /* One weighted pick in row [b,e).  Returns the absolute edge index or -1. */
 static int64_t sample_row(const fwo_ctx* c, int64_t b, int64_t e, int k,
                           int32_t prev, uint64_t qid) {
@@ -182,26 +205,14 @@ static int64_t sample_row(const fwo_ctx* c, int64_t b, int64_t e, int k,
     if (best == ~(uint64_t)0) return -1;
     return 4 * q0 + (int64_t)(uint32_t)best;
   }
-  /* strips: group B = (s,l) holds quads s*128 + j*32 + l, j = 0..3 */
-  const int64_t nsuper = (nq + 127) >> 7;
+  /* strips: group B = (s,l) holds quads s*512 + j*32 + l, j = 0..15 */
+  const int64_t nsuper = (nq + 511) >> 9;
+  float w64[64];
+  int64_t i64[64];
   for (int64_t s = 0; s < nsuper; ++s) {
     for (int l = 0; l < 32; ++l) {
-      float S[4];
-      int any = 0;
-      for (int j = 0; j < 4; ++j) {
-        int64_t q = s * 128 + j * 32 + l;
-        float w4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (q < nq) {
-          for (int cc = 0; cc < 4; ++cc) {
-            int64_t i = 4 * (q0 + q) + cc;
-            if (i >= b && i < e) w4[cc] = bias_of(c, i, k, prev);
-          }
-          any = 1;
-        }
-        S[j] = (w4[0] + w4[1]) + (w4[2] + w4[3]);
-      }
-      if (!any) continue;
-      float W = (S[0] + S[1]) + (S[2] + S[3]);
+      if (s * 512 + l >= nq) continue;  /* the strip has no quad inside the row */
+      float W = strip_fill(c, b, e, q0, nq, s, l, k, prev, w64, i64);
       if (!(W > 0.0f)) continue;
       uint32_t B = (uint32_t)(s * 32 + l);
       ctr[0] = (uint32_t)((s / 3) * 32 + l);  /* one block serves supergroups 3g..3g+2 of lane l */
@@ -219,27 +230,15 @@ static int64_t sample_row(const fwo_ctx* c, int64_t b, int64_t e, int k,
   int l = (int)(B & 31u);
   ctr[0] = (uint32_t)((s / 3) * 32 + l);
   fwo_philox4x32_10(ctr, c->key, r);
-  float w16[16];
-  int64_t i16[16];
-  float S[4];
-  for (int j = 0; j < 4; ++j) {
-    int64_t q = s * 128 + j * 32 + l;
-    for (int cc = 0; cc < 4; ++cc) {
-      int64_t i = 4 * (q0 + q) + cc;
-      i16[4 * j + cc] = i;
-      w16[4 * j + cc] = (q < nq && i >= b && i < e) ? bias_of(c, i, k, prev) : 0.f;
-    }
-    S[j] = (w16[4 * j] + w16[4 * j + 1]) + (w16[4 * j + 2] + w16[4 * j + 3]);
-  }
-  float W = (S[0] + S[1]) + (S[2] + S[3]);
+  float W = strip_fill(c, b, e, q0, nq, s, l, k, prev, w64, i64);
   float u = (float)(r[3] >> 8) * 0x1p-24f;
   float t = u * W;
   float acc = 0.f;
   int64_t last = -1;
-  for (int z = 0; z < 16; ++z) {
-    if (w16[z] > 0.f) {
-      last = i16[z];
-      acc = acc + w16[z];
+  for (int z = 0; z < 64; ++z) {
+    if (w64[z] > 0.f) {
+      last = i64[z];
+      acc = acc + w64[z];
       if (acc > t) return last;
     }
   }
@@ -290,7 +289,7 @@ int fwo_walk(int64_t V, const void* xadj, int xadj_bits, const int32_t* adj,
              uint64_t* stats, int threads) {
   if (V < 0 || n < 0 || d < 0 || d >= (1 << 28)) return -1;
   if (xadj_bits != 32 && xadj_bits != 64) return -2;
-  if (group_mode != 1 && group_mode != 16) return -3;
+  if (group_mode != 1 && group_mode != 64) return -3;
   if (app < 0 || app > 3) return -4;
   if (app == FWO_APP_METAPATH && (!label || !schema || schema_len <= 0)) return -5;
   if (app != FWO_APP_METAPATH && !weight) return -6;

@@ -36,7 +36,7 @@ def main():
     starts = graphs.config1_starts()
     out = {"starts": starts, "graph_sha256": np.array(graph_digest(g))}
     for name, app, kw in CASES:
-        for mode in (1, 16):
+        for mode in (1, 64):
             res, steps, scanned, hist = O.graph_walk(g, app, starts, seed=1337, group_mode=mode, **kw)
             out["%s_g%d" % (name, mode)] = res
             out["%s_g%d_stats" % (name, mode)] = np.array([steps, scanned], dtype=np.uint64)

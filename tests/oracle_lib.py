@@ -35,7 +35,7 @@ def philox(ctr, key):
 
 
 def walk(xadj, adj, weight, label, app, starts, d=80, tp=0.2, p=2.0, q=0.5, schema=None,
-         seed=1337, query_id_base=0, group_mode=16, threads=0):
+         seed=1337, query_id_base=0, group_mode=64, threads=0):
     """Returns (result[n, d+1] int32, steps, scanned, len_hist[d+1])."""
     xadj = np.ascontiguousarray(xadj)
     assert xadj.dtype in (np.dtype(np.uint32), np.dtype(np.int64))

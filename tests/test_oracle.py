@@ -56,7 +56,7 @@ def test_golden_fixtures():
     cases = [("deepwalk", 0, dict(d=80)), ("ppr", 1, dict(d=80, tp=0.2)),
              ("node2vec", 2, dict(d=80, p=2.0, q=0.5)), ("metapath", 3, dict(d=5, schema=[0, 1, 2, 3, 4]))]
     for name, app, kw in cases:
-        for mode in (1, 16):
+        for mode in (1, 64):
             res, steps, scanned, _ = O.graph_walk(g, app, starts, seed=1337, group_mode=mode, **kw)
             assert (res == gold["%s_g%d" % (name, mode)]).all(), (name, mode)
             assert [steps, scanned] == gold["%s_g%d_stats" % (name, mode)].tolist()
@@ -66,7 +66,7 @@ def _small_graph():
     return fw.rmat(8, 3000, weight_range=(1.0, 5.0), n_labels=5)
 
 
-@pytest.mark.parametrize("mode", [1, 16])
+@pytest.mark.parametrize("mode", [1, 64])
 @pytest.mark.parametrize("app,kw", [(0, dict(d=8)), (1, dict(d=8, tp=0.2)), (2, dict(d=8, p=2.0, q=0.5)),
                                     (2, dict(d=8, p=0.25, q=4.0)), (3, dict(d=5, schema=[0, 1, 2, 3, 4])),
                                     (3, dict(d=6, schema=[2, 2, 0]))])
@@ -94,7 +94,7 @@ def test_big_row_law_both_modes():
     V = deg + 2
     assert len(xadj) == V + 1
     n = 200000
-    for mode in (1, 16):
+    for mode in (1, 64):
         res, _, _, _ = O.walk(xadj, adj, weight, None, 0, np.ones(n, dtype=np.int32), d=1, group_mode=mode)
         obs = np.bincount(res[:, 1] - 2, minlength=deg).astype(np.float64)
         exp = n * w.astype(np.float64) / w.astype(np.float64).sum()
