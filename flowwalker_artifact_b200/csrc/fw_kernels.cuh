@@ -27,14 +27,23 @@ constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared
 #ifndef FW_STAGES
 #define FW_STAGES 2
 #endif
+// node2vec sweeps long rows with direct loads: its time goes into the membership test, whose
+// dependent loads are hidden by resident warps, and without the ring's 8 KB per warp four CTAs
+// fit on an SM instead of three (measured 377 ms vs 518 ms on an R-MAT scale-20 graph).
+#ifndef FW_N2V_RING
+#define FW_N2V_RING 0
+#endif
 #ifndef FW_N2V_MIN_BLOCKS
-#define FW_N2V_MIN_BLOCKS 3
+#define FW_N2V_MIN_BLOCKS 4
 #endif
 #ifndef FW_MIN_BLOCKS
 #define FW_MIN_BLOCKS 5
 #endif
 constexpr int kStages = FW_STAGES;       // ring depth per warp
 constexpr uint32_t kSubBytes = 16u * fw::kQuadsPerSub;  // 2 KB: one ring stage, one bulk copy
+// whether an app sweeps long rows through the shared-memory ring
+template <int APP>
+__host__ __device__ constexpr bool uses_ring() { return APP != FW_APP_NODE2VEC || FW_N2V_RING != 0; }
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls of an mbarrier before giving up
 
 // Scratch words (uint64) in device memory.
@@ -483,7 +492,8 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   // combined as (A0+A1)+(A2+A3) and tested once per supergroup.
   const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
   const uint32_t last_b = nb - 1u;
-  if (nb >= 3u && lane == 0) {
+  const bool ringed = uses_ring<APP>() && nb >= 3u;
+  if (ringed && lane == 0) {
 #pragma unroll
     for (uint32_t t = 0; t < kStages; ++t)
       if (1u + t < last_b) ring_fill<APP>(c, ring, 1u + t, t);
@@ -508,7 +518,10 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     }
   };
   absorb(sub_global<APP, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false);
-  if (nb >= 3u) {
+  if (!ringed) {
+#pragma unroll 1
+    for (uint32_t b = 1; b < last_b; ++b) absorb(sub_global<APP, CLEAN>(a, c, b, lane), b, false, true);
+  } else {
     uint32_t t = 0;
     // Kept rolled on purpose: an unrolled sweep measured slower (instruction cache shared by
     // 40 warps that sit at different places of the kernel).
@@ -594,7 +607,7 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-  constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_STRIP ? kStages * stage_bytes<APP>() : 0u;
+  constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_STRIP && uses_ring<APP>() ? kStages * stage_bytes<APP>() : 0u;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
   Ring ring;
@@ -719,7 +732,7 @@ inline KernelFn pick_kernel(int app, int mode, bool clean, int xadj_bits) {
 // Dynamic shared memory of one CTA: the warps' rings, then the histogram.
 inline size_t kernel_smem_bytes(int app, int mode, int d, bool hist_in_smem) {
   size_t ring = 0;
-  if (mode != FW_GROUP_EDGE)
+  if (mode != FW_GROUP_EDGE && (app != FW_APP_NODE2VEC || FW_N2V_RING != 0))
     ring = (size_t)kWarpsPerCta * kStages * (app == FW_APP_NODE2VEC ? 2u * kSubBytes : kSubBytes);
   return ring + (hist_in_smem ? (size_t)(d + 1) * 4 : 0);
 }

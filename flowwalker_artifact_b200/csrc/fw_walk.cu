@@ -389,6 +389,43 @@ extern "C" int fw_walk_batch(fw_engine* e, const fw_walk_params* p, const int32_
 }
 
 // ---------------------------------------------------------------------------
+// Self-test of the bounded wait
+// ---------------------------------------------------------------------------
+namespace {
+// One warp waits on an mbarrier that nothing ever arrives at, with the same polling loop the
+// ring uses but a caller-chosen limit; it must come back and report, not spin.
+__global__ void wait_timeout_probe(uint32_t polls, unsigned int* out) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t addr = smem_addr(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(addr, 1u);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  bool done = false;
+  for (uint32_t i = 0; i < polls && !done; ++i) done = mbar_try_wait(addr, 0u) != 0;
+  if (!done && threadIdx.x == 0) atomicOr(out, FW_STATUS_WAIT_TIMEOUT);
+}
+}  // namespace
+
+extern "C" int fw_selftest_wait_timeout(int device, uint32_t polls, uint32_t* status) {
+  fw::clear_error();
+  if (!status) return fw::fail(FW_ERR_ARG, "fw_selftest_wait_timeout: null argument");
+  if (polls == 0 || polls > (1u << 20)) return fw::fail(FW_ERR_ARG, "polls must be in 1..2^20");
+  DeviceGuard guard(device);
+  unsigned int* d = nullptr;
+  FW_CUDA(cudaMalloc(&d, sizeof(unsigned int)));
+  cudaError_t err = cudaMemset(d, 0, sizeof(unsigned int));
+  if (err == cudaSuccess) { wait_timeout_probe<<<1, 32>>>(polls, d); err = cudaGetLastError(); }
+  unsigned int h = 0;
+  if (err == cudaSuccess) err = cudaMemcpy(&h, d, sizeof(h), cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  if (err != cudaSuccess) return fw::fail(FW_ERR_CUDA, "wait self-test failed: %s", cudaGetErrorString(err));
+  *status = h;
+  return FW_OK;
+}
+
+// ---------------------------------------------------------------------------
 // Allocation-free entry point
 // ---------------------------------------------------------------------------
 //

@@ -162,6 +162,15 @@ int fw_walk_batch(fw_engine* e, const fw_walk_params* params, const int32_t* sta
 void fw_free_pinned(void* p);
 
 /*
+ * Failure-detection self-test, no counterpart in the reference (whose device waits are
+ * unbounded and whose host code exits on any CUDA error, include/util.cuh:56-68).  One warp
+ * waits on a barrier that nothing completes, with the same bounded polling loop the staging
+ * ring uses and `polls` as the limit; *status receives FW_STATUS_WAIT_TIMEOUT and the context
+ * stays usable.
+ */
+int fw_selftest_wait_timeout(int device, uint32_t polls, uint32_t* status);
+
+/*
  * Allocation-free walk.  No counterpart in the reference (its host code
  * allocates at every call, src/walk.cu:98-138, 586).
  *

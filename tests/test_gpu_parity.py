@@ -109,3 +109,17 @@ def test_shards_union_equals_single_run():
     out, st = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=128)
     assert (out == full).all() and st.launches == 8
     eng.close()
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A wait that nothing completes runs out after its poll limit, sets the status word and
+    leaves the context usable (the next walk still matches the golden walker)."""
+    import ctypes
+    L = fw.lib()
+    L.fw_selftest_wait_timeout.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint32)]
+    status = ctypes.c_uint32(0)
+    assert L.fw_selftest_wait_timeout(0, 2000, ctypes.byref(status)) == 0, L.fw_last_error()
+    assert status.value == 4  # FW_STATUS_WAIT_TIMEOUT
+    g = graphs.config1()
+    arrs = dict(xadj=g.xadj.copy(), adj=g.adj.copy(), weight=g.weight.copy(), label=g.label.copy())
+    assert_same(run_both(arrs, fw.APP_DEEPWALK, dict(d=20), graphs.config1_starts(), fw.GROUP_STRIP))
