@@ -106,10 +106,10 @@ class ClockSampler:
 
 
 # DRAM bytes per algorithmic byte of the DeepWalk config-2 launch, from the ncu capture summarised
-# in profiles/walk_kernel_deepwalk_scale22_tma_ring.md (dram__bytes_read.sum + write.sum = 52.97 GB
-# for 249.05 GB algorithmic on a 1,000,000-query launch of the same graph; both grow in proportion
+# in profiles/walk_kernel_deepwalk_scale22_tma_ring_strip64.md (dram__bytes_read.sum + write.sum = 53.07 GB
+# for 249.08 GB algorithmic on a 1,000,000-query launch of the same graph; both grow in proportion
 # with the number of queries).  Only valid for that workload: other runs report traffic = null.
-DRAM_PER_ALGORITHMIC_BYTE = 0.2127
+DRAM_PER_ALGORITHMIC_BYTE = 0.2131
 
 
 def algorithmic_bytes(app, scanned, steps, n, xadj_bits):
