@@ -425,6 +425,98 @@ __device__ __forceinline__ bool ring_sub(const WalkArgs& a, const StepCtx& c, ui
   return true;
 }
 
+// A lane's running state while a row is swept: the partial sums of the current supergroup
+// and the Philox block that serves it.
+struct SuperAcc {
+  float p01, a2;   // A0+A1 and A2 of the supergroup in progress
+  uint32_t g, m;   // its Philox block (supergroup index / 3) and word (index mod 3)
+  fw::Philox4 r;
+};
+
+// Adds sub-block b's partial sum A; at the end of a supergroup (or of the row) forms the strip's
+// total (A0+A1)+(A2+A3) and tests its key, behind the lower-bound filter when `filtered`.
+__device__ __forceinline__ void absorb(const WalkArgs& a, SuperAcc& s, Best& best, float A, uint32_t b, bool row_end,
+                                       bool filtered, uint32_t lane, uint32_t c1, uint32_t qlo, uint32_t qhi) {
+  const uint32_t u = b & 3u;
+  if (u == 0u) s.p01 = A;
+  else if (u == 1u) s.p01 = __fadd_rn(s.p01, A);
+  else if (u == 2u) s.a2 = A;
+  if (u == 3u || row_end) {
+    const float W = u == 3u ? __fadd_rn(s.p01, __fadd_rn(s.a2, A)) : u == 2u ? __fadd_rn(s.p01, s.a2) : s.p01;
+    const uint32_t x = s.m == 0u ? s.r.x : s.m == 1u ? s.r.y : s.r.z;
+    const uint32_t id = (b >> 2) * 32u + lane;
+    if (filtered) offer_filtered(best, x, s.r.w, W, id, __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key)));
+    else offer(best, x, s.r.w, W, id);
+    if (!row_end) {
+      if (++s.m == 3u) { s.m = 0u; s.r = fw::philox4x32_10((++s.g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
+    }
+  }
+}
+
+// Inverse-CDF pick inside the winning strip B (every lane computes the same): the first of
+// its edges in canonical order (quad j, edge k) whose running sum exceeds u * W, u from the pick
+// word.  Zero biases leave the running sum unchanged, so counting the sums <= u * W gives that
+// edge's position.  Returns the edge index relative to quad 0 of the row.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ uint32_t pick_in_row(const WalkArgs& a, const StepCtx& c, uint32_t B, uint32_t pick,
+                                                float W, uint32_t lane) {
+  const uint32_t sB = B >> 5, lB = B & 31u;
+  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
+  const uint32_t last_blk = (c.nq - 1u) >> 5;
+  const uint32_t blk0 = 16u * sB;
+  const uint32_t nblk = min(16u, last_blk - blk0 + 1u);
+  if (APP == FW_APP_NODE2VEC) c.from = 0u;  // the strip may lie before the blocks just visited
+  float acc = 0.0f;
+  uint32_t cnt = 0, j = 0;
+#pragma unroll 1
+  for (; j < nblk; ++j) {
+    const uint32_t blk = blk0 + j;
+    const bool edge_blk = blk == 0u || blk == last_blk;
+    float4 v;
+    if (APP == FW_APP_NODE2VEC) {
+      // the membership test works on whole blocks: load the block as a warp, take lane lB's quad
+      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
+      v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
+      v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
+      v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
+      v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
+    } else {
+      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
+    }
+    acc = __fadd_rn(acc, v.x); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, v.y); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, v.z); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, v.w); cnt += acc <= thr ? 1u : 0u;
+    if (cnt < 4u * (j + 1u)) break;  // found (warp-uniform)
+  }
+  if (j == nblk) {
+    // rounding pushed u * W past the sequential total: take the strip's last positive edge
+    if (APP == FW_APP_NODE2VEC) c.from = 0u;
+    cnt = 0;
+#pragma unroll 1
+    for (j = 0; j < nblk; ++j) {
+      const uint32_t blk = blk0 + j;
+      const bool edge_blk = blk == 0u || blk == last_blk;
+      float4 v;
+      if (APP == FW_APP_NODE2VEC) {
+        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
+        v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
+        v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
+        v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
+        v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
+      } else {
+        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
+      }
+      if (v.x > 0.0f) cnt = 4u * j;
+      if (v.y > 0.0f) cnt = 4u * j + 1u;
+      if (v.z > 0.0f) cnt = 4u * j + 2u;
+      if (v.w > 0.0f) cnt = 4u * j + 3u;
+    }
+  }
+  return 4u * (32u * (blk0 + (cnt >> 2)) + lB) + (cnt & 3u);
+}
+
+
 // One weighted pick in the row described by c, by one warp.  Returns the
 // edge index relative to quad 0 of the row, or 0xFFFFFFFF when no edge has
 // positive bias.
@@ -498,29 +590,12 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     for (uint32_t t = 0; t < kStages; ++t)
       if (1u + t < last_b) ring_fill<APP>(c, ring, 1u + t, t);
   }
-  uint32_t g = 0, m = 0;  // Philox block of the current supergroup, supergroup index mod 3
-  float p01 = 0.0f, a2 = 0.0f;
-  // Adds sub-block b's partial sum; at the end of a supergroup (or of the row) tests its key.
-  auto absorb = [&](float A, uint32_t b, bool row_end, bool filtered) {
-    const uint32_t u = b & 3u;
-    if (u == 0u) p01 = A;
-    else if (u == 1u) p01 = __fadd_rn(p01, A);
-    else if (u == 2u) a2 = A;
-    if (u == 3u || row_end) {
-      const float W = u == 3u ? __fadd_rn(p01, __fadd_rn(a2, A)) : u == 2u ? __fadd_rn(p01, a2) : p01;
-      const uint32_t x = m == 0u ? r.x : m == 1u ? r.y : r.z;
-      const uint32_t id = (b >> 2) * 32u + lane;
-      if (filtered) offer_filtered(best, x, r.w, W, id, __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key)));
-      else offer(best, x, r.w, W, id);
-      if (!row_end) {
-        if (++m == 3u) { m = 0u; r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
-      }
-    }
-  };
-  absorb(sub_global<APP, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false);
+  SuperAcc acc{0.0f, 0.0f, 0u, 0u, r};
+  absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
   if (!ringed) {
 #pragma unroll 1
-    for (uint32_t b = 1; b < last_b; ++b) absorb(sub_global<APP, CLEAN>(a, c, b, lane), b, false, true);
+    for (uint32_t b = 1; b < last_b; ++b)
+      absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, b, lane), b, false, true, lane, c1, qlo, qhi);
   } else {
     uint32_t t = 0;
     // Kept rolled on purpose: an unrolled sweep measured slower (instruction cache shared by
@@ -532,73 +607,17 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
         ring.failed = true;
         return 0xFFFFFFFFu;
       }
-      absorb(A, b, false, true);
+      absorb(a, acc, best, A, b, false, true, lane, c1, qlo, qhi);
       t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
     }
   }
-  if (nb > 1u) absorb(sub_global<APP, CLEAN>(a, c, last_b, lane), last_b, true, false);
+  if (nb > 1u) absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, last_b, lane), last_b, true, false, lane, c1, qlo, qhi);
   warp_argmin(best.key, best.id);
   if (best.id == 0xFFFFFFFFu) return best.id;
 
-  // Inverse-CDF pick inside the winning strip B (every lane computes the same): the first of
-  // its edges in canonical order (quad j, edge k) whose running sum exceeds u * W.  Zero biases
-  // leave the running sum unchanged, so counting the sums <= u * W gives that edge's position.
-  const uint32_t B = best.id, sB = B >> 5, lB = B & 31u;
-  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)lB);
-  const float W = __shfl_sync(0xFFFFFFFFu, best.W, (int)lB);
-  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
-  const uint32_t last_blk = (c.nq - 1u) >> 5;
-  const uint32_t blk0 = 16u * sB;
-  const uint32_t nblk = min(16u, last_blk - blk0 + 1u);
-  if (APP == FW_APP_NODE2VEC) c.from = 0u;  // the strip may lie before the blocks just visited
-  float acc = 0.0f;
-  uint32_t cnt = 0, j = 0;
-#pragma unroll 1
-  for (; j < nblk; ++j) {
-    const uint32_t blk = blk0 + j;
-    const bool edge_blk = blk == 0u || blk == last_blk;
-    float4 v;
-    if (APP == FW_APP_NODE2VEC) {
-      // the membership test works on whole blocks: load the block as a warp, take lane lB's quad
-      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
-      v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
-      v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
-      v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
-      v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
-    } else {
-      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
-    }
-    acc = __fadd_rn(acc, v.x); cnt += acc <= thr ? 1u : 0u;
-    acc = __fadd_rn(acc, v.y); cnt += acc <= thr ? 1u : 0u;
-    acc = __fadd_rn(acc, v.z); cnt += acc <= thr ? 1u : 0u;
-    acc = __fadd_rn(acc, v.w); cnt += acc <= thr ? 1u : 0u;
-    if (cnt < 4u * (j + 1u)) break;  // found (warp-uniform)
-  }
-  if (j == nblk) {
-    // rounding pushed u * W past the sequential total: take the strip's last positive edge
-    if (APP == FW_APP_NODE2VEC) c.from = 0u;
-    cnt = 0;
-#pragma unroll 1
-    for (j = 0; j < nblk; ++j) {
-      const uint32_t blk = blk0 + j;
-      const bool edge_blk = blk == 0u || blk == last_blk;
-      float4 v;
-      if (APP == FW_APP_NODE2VEC) {
-        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
-        v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
-        v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
-        v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
-        v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
-      } else {
-        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
-      }
-      if (v.x > 0.0f) cnt = 4u * j;
-      if (v.y > 0.0f) cnt = 4u * j + 1u;
-      if (v.z > 0.0f) cnt = 4u * j + 2u;
-      if (v.w > 0.0f) cnt = 4u * j + 3u;
-    }
-  }
-  return 4u * (32u * (blk0 + (cnt >> 2)) + lB) + (cnt & 3u);
+  const uint32_t B = best.id;
+  return pick_in_row<APP, CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)),
+                                 __shfl_sync(0xFFFFFFFFu, best.W, (int)(B & 31u)), lane);
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
