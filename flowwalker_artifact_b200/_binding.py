@@ -71,6 +71,7 @@ def lib():
         L.fw_engine_destroy.argtypes = [vp]
         L.fw_engine_destroy.restype = None
         L.fw_engine_device.argtypes = [vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+        L.fw_engine_set_sharing.argtypes = [vp, ctypes.c_int]
         L.fw_walk_device.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, vp,
                                      ctypes.POINTER(WalkStats), vp]
         L.fw_walk.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, ctypes.POINTER(WalkStats), vp]
@@ -190,6 +191,10 @@ class Engine:
         dev, sms = ctypes.c_int(), ctypes.c_int()
         _check(lib().fw_engine_device(self._h, dev, sms))
         self.device, self.sm_count = dev.value, sms.value
+
+    def set_sharing(self, mode):
+        """-1: by max degree (default), 0: never, 1: always share very long rows between warps."""
+        _check(lib().fw_engine_set_sharing(self._h, mode))
 
     def walk(self, params, starts, want_hist=False):
         """Host buffers in, host result out (fw_walk)."""

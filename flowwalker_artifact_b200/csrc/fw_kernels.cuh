@@ -517,13 +517,229 @@ __device__ __forceinline__ uint32_t pick_in_row(const WalkArgs& a, const StepCtx
 }
 
 
+// ---- CTA-cooperative sweep of very long rows (the block-granularity sampler) ----
+//
+// When a warp meets a row of at least kCoopMinSupers supergroups while other warps of its CTA
+// have run out of queries, it posts the row on the CTA's board.  The owner keeps sweeping from
+// the front with its usual loop; idle warps draw tickets and take chunks of full interior
+// supergroups from the back (ticket k covers the kCoopChunkSupers supergroups below
+// end_super - k * kCoopChunkSupers).  At every supergroup boundary the owner looks at the ticket
+// count and stops where the helpers' part begins.  Helpers fold their best (key, strip id) into
+// the board with one 64-bit atomicMin: the block-level combine.  min over (key, id) is
+// order-independent and idempotent, so overlaps are harmless and the walk is bit-identical to the
+// single-warp sweep.  Busy warps never help: that was measured and nearly halved the throughput
+// of the bulk phase.  Stands in for sampler_block (include/sampler.cuh:87-127) and the block
+// phase of the reference scheduler (include/walker.cuh:1397-1419), which stalls the whole CTA on
+// one query at a time.
+// Kernel variant (template MODE) of the strip sampler whose warps also share very long rows: kept
+// apart because the sharing code costs the plain sweep registers (48 against 40, one CTA per SM less)
+// and about 20 % of its throughput; the engine selects it for graphs that have rows long enough to
+// leave a tail.
+constexpr int kModeStripShared = FW_GROUP_STRIP + 1;
+constexpr uint32_t kCoopMinSupers = 16;   // rows from 16 supergroups (about 32,000 edges) may be shared
+constexpr uint32_t kCoopChunkSupers = 4;  // supergroups per ticket (32 KB)
+constexpr uint32_t kCoopSpinLimit = 1u << 22;
+constexpr unsigned int kCoopClosed = 0xFFFF0000u;  // ticket word while no row is posted (epoch 0xFFFF is never used)
+constexpr unsigned long long kCoopFailed = 0xFFFFFFFFFFFFFFFEull;
+
+struct CoopTask {
+  unsigned int walking;   // warps of the CTA that still have queries of their own
+  unsigned int lock;      // 1 while a warp owns the board
+  unsigned int open;      // 1 while a row is posted
+  unsigned int ticket;    // epoch << 16 | tickets drawn; drawn with atomicAdd
+  unsigned int epoch;     // epoch of the posted row, 0 .. 0xFFFE
+  unsigned int done;      // tickets served
+  unsigned int end_super; // the shared supergroups are [1, end_super), handed out from the back
+  unsigned long long best;  // key bits << 32 | strip id, atomicMin
+  uint32_t c1, qlo, qhi;
+  StepCtx c;              // the row; `from` and `flags` are per helper
+};
+
+__device__ __forceinline__ unsigned int ld_volatile(const unsigned int* p) {
+  return *reinterpret_cast<const volatile unsigned int*>(p);
+}
+
+// Full interior supergroups [s0, s1) of the row c (every sub-block complete, no boundary quad),
+// by one warp.  False when a staged copy did not arrive in time.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ bool sweep_supers(const WalkArgs& a, const StepCtx& c, uint32_t s0, uint32_t s1,
+                                             uint32_t lane, uint32_t c1, uint32_t qlo, uint32_t qhi, Ring& ring,
+                                             const unsigned char* ring_ptr, Best& best) {
+  const uint32_t b0 = 4u * s0, bend = 4u * s1;
+  if (uses_ring<APP>() && lane == 0) {
+#pragma unroll
+    for (uint32_t t = 0; t < kStages; ++t)
+      if (b0 + t < bend) ring_fill<APP>(c, ring, b0 + t, t);
+  }
+  SuperAcc acc{0.0f, 0.0f, s0 / 3u, s0 % 3u, fw::Philox4{0u, 0u, 0u, 0u}};
+  acc.r = fw::philox4x32_10(acc.g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+  uint32_t t = 0;
+#pragma unroll 1
+  for (uint32_t b = b0; b < bend; ++b) {
+    float A;
+    if (uses_ring<APP>()) {
+      if (!ring_sub<APP, CLEAN>(a, c, b, bend, lane, ring, ring_ptr, t, A)) return false;
+      t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
+    } else {
+      A = sub_global<APP, CLEAN>(a, c, b, lane);
+    }
+    absorb(a, acc, best, A, b, false, true, lane, c1, qlo, qhi);
+  }
+  return true;
+}
+
+// An idle warp serves tickets of the posted row until they stop being valid.  Every lane of the
+// warp must call it.  Returns the warp's ring parity in bits 1.., and in bit 0 whether all went
+// well (0: a staged copy did not arrive).  Out of line: only idle warps run it.
+template <int APP, bool CLEAN>
+__device__ __noinline__ uint32_t coop_serve(const WalkArgs& args, CoopTask* task, uint32_t lane, Ring ring,
+                                            const unsigned char* ring_ptr, uint32_t* my_flags) {
+  WalkArgs a;  // the kernel arguments arrive by address here: read the few fields the sweep needs once
+  a.adj = args.adj; a.inv_p = args.inv_p; a.inv_q = args.inv_q; a.k0 = args.k0; a.k1 = args.k1;
+  for (;;) {
+    unsigned int tk = 0, mine = 0;
+    if (lane == 0) {
+      tk = atomicAdd(&task->ticket, 1u);
+      __threadfence_block();
+      // a ticket belongs to the row whose epoch it carries; that row stays posted until every
+      // ticket drawn from its counter has been served
+      mine = (tk >> 16) == ld_volatile(&task->epoch);
+    }
+    tk = __shfl_sync(0xFFFFFFFFu, tk, 0);
+    if (!__shfl_sync(0xFFFFFFFFu, mine, 0)) return (ring.parity << 1) | 1u;
+    const uint32_t k = tk & 0xFFFFu;
+    const uint32_t end_super = task->end_super;
+    const uint32_t below = k * kCoopChunkSupers;
+    Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
+    bool fine = true;
+    if (below + 1u < end_super) {  // something is left above supergroup 0
+      const uint32_t s1 = end_super - below;
+      const uint32_t s0 = s1 > kCoopChunkSupers + 1u ? s1 - kCoopChunkSupers : 1u;
+      StepCtx c = task->c;
+      c.flags = my_flags;
+      if (APP == FW_APP_NODE2VEC && c.prev >= 0) {
+        // the membership windows chain through the row in ascending order: start this chunk's
+        // chain at the first entry of prev's row that is not below the chunk's first neighbour id
+        int32_t first = 0;
+        if (lane == 0) first = __ldg(reinterpret_cast<const int32_t*>(c.sec + (size_t)s0 * fw::kQuadsPerSuper));
+        first = __shfl_sync(0xFFFFFFFFu, first, 0);
+        c.from = warp_lower_bound(c.prow, 0u, c.plen, first, lane);
+      }
+      fine = sweep_supers<APP, CLEAN>(a, c, s0, s1, lane, task->c1, task->qlo, task->qhi, ring, ring_ptr, best);
+      warp_argmin(best.key, best.id);
+    }
+    else __nanosleep(512);  // nothing left above the owner's part: do not hammer the ticket counter
+    if (lane == 0) {
+      if (fine && best.id != 0xFFFFFFFFu) atomicMin(&task->best, ((unsigned long long)best.key << 32) | best.id);
+      __threadfence_block();
+      if (fine) atomicAdd(&task->done, 1u);
+    }
+    if (!fine) return ring.parity << 1;
+  }
+}
+
+// A warp out of queries: lend a hand if a row is posted.  False when a staged copy did not arrive.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ bool coop_help(const WalkArgs& a, CoopTask* task, uint32_t lane, Ring& ring,
+                                          const unsigned char* ring_ptr, uint32_t* my_flags) {
+  unsigned int open = 0;
+  if (lane == 0) open = ld_volatile(&task->open);
+  if (!__shfl_sync(0xFFFFFFFFu, open, 0)) return true;
+  const uint32_t r = coop_serve<APP, CLEAN>(a, task, lane, ring, ring_ptr, my_flags);
+  ring.parity = r >> 1;
+  return (r & 1u) != 0;
+}
+
+// Owner: posts the row when an idle warp exists and the board is free.  Out of line (rare).
+__device__ __noinline__ unsigned int coop_post(CoopTask* task, const int4* prim, const int4* sec, uint32_t nq,
+                                               uint32_t head, uint32_t tail, int32_t prev, const int32_t* prow,
+                                               uint32_t plen, int32_t want, uint32_t c1, uint32_t qlo, uint32_t qhi,
+                                               uint32_t end_super, uint32_t lane) {
+  unsigned int got = 0;
+  if (lane == 0 && ld_volatile(&task->walking) < (unsigned int)kWarpsPerCta && atomicCAS(&task->lock, 0u, 1u) == 0u) {
+    got = 1;
+    unsigned int ep = ld_volatile(&task->epoch) + 1u;
+    if (ep >= 0xFFFFu) ep = 0u;
+    StepCtx c;
+    c.prim = prim; c.sec = sec; c.nq = nq; c.head = head; c.tail = tail; c.prev = prev;
+    c.prow = prow; c.plen = plen; c.want = want; c.from = 0u; c.flags = nullptr;
+    task->c = c;
+    task->c1 = c1; task->qlo = qlo; task->qhi = qhi;
+    task->end_super = end_super;
+    task->done = 0u;
+    task->best = ~0ull;
+    task->epoch = ep;
+    __threadfence_block();
+    atomicExch(&task->ticket, ep << 16);
+    __threadfence_block();
+    atomicExch(&task->open, 1u);
+  }
+  return __shfl_sync(0xFFFFFFFFu, got, 0);
+}
+
+// Owner: no more tickets for this row; returns how many were drawn.
+__device__ __forceinline__ uint32_t coop_stop_tickets(CoopTask* task, uint32_t lane) {
+  unsigned int k = 0;
+  if (lane == 0) {
+    atomicExch(&task->open, 0u);
+    k = atomicExch(&task->ticket, kCoopClosed) & 0xFFFFu;
+  }
+  return __shfl_sync(0xFFFFFFFFu, k, 0);
+}
+
+// Owner: waits (bounded) until the drawn tickets are served, folds the helpers' result into its
+// own packed (key, id) and frees the board.  kCoopFailed when the wait ran out.  Out of line.
+__device__ __noinline__ unsigned long long coop_close(CoopTask* task, uint32_t tickets, unsigned long long own,
+                                                      uint32_t lane) {
+  unsigned long long fin = kCoopFailed;
+  if (lane == 0) {
+    for (uint32_t spin = 0; spin < kCoopSpinLimit; ++spin) {
+      if (ld_volatile(&task->done) >= tickets) { fin = own; break; }
+      __nanosleep(64);
+    }
+    __threadfence_block();
+    if (fin != kCoopFailed) {
+      const unsigned long long theirs = *reinterpret_cast<volatile unsigned long long*>(&task->best);
+      if (theirs < fin) fin = theirs;
+    }
+    __threadfence_block();
+    if (fin != kCoopFailed) atomicExch(&task->lock, 0u);  // after a failed wait the board stays taken
+  }
+  return __shfl_sync(0xFFFFFFFFu, fin, 0);
+}
+
+// Owner: total bias and pick word of strip B when another warp reduced it.  Out of line (rare).
+// Returns the pick word in the high half and the bits of the total in the low half.
+template <int APP, bool CLEAN>
+__device__ __noinline__ unsigned long long strip_redo(const WalkArgs& args, StepCtx c, uint32_t B, uint32_t c1,
+                                                      uint32_t qlo, uint32_t qhi, uint32_t lane) {
+  WalkArgs a;
+  a.adj = args.adj; a.inv_p = args.inv_p; a.inv_q = args.inv_q; a.k0 = args.k0; a.k1 = args.k1;
+  const uint32_t sW = B >> 5, lW = B & 31u;
+  const uint32_t last_b = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub - 1u;
+  const uint32_t pick = fw::philox4x32_10((sW / 3u) * 32u + lW, c1, qlo, qhi, a.k0, a.k1).w;
+  if (APP == FW_APP_NODE2VEC) c.from = 0u;
+  float A[4];
+#pragma unroll 1
+  for (uint32_t i = 0; i < 4u; ++i) {
+    const uint32_t b = 4u * sW + i;
+    A[i] = 0.0f;
+    if (b <= last_b) {  // warp-uniform
+      A[i] = sub_global<APP, CLEAN>(a, c, b, APP == FW_APP_NODE2VEC ? lane : lW);
+      if (APP == FW_APP_NODE2VEC) A[i] = __shfl_sync(0xFFFFFFFFu, A[i], (int)lW);
+    }
+  }
+  const float W = __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3]));
+  return ((unsigned long long)pick << 32) | __float_as_uint(W);
+}
+
 // One weighted pick in the row described by c, by one warp.  Returns the
 // edge index relative to quad 0 of the row, or 0xFFFFFFFF when no edge has
 // positive bias.
 template <int APP, int MODE, bool CLEAN>
 __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const StepCtx& c, uint32_t step,
                                                     uint32_t qlo, uint32_t qhi, uint32_t lane, Ring& ring,
-                                                    const unsigned char* ring_ptr) {
+                                                    const unsigned char* ring_ptr, CoopTask* task) {
   const uint32_t c1 = step | (fw::kPurposeScan << 28);
   const int4 zero = make_int4(0, 0, 0, 0);
   if (MODE == FW_GROUP_EDGE) {
@@ -591,17 +807,43 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
       if (1u + t < last_b) ring_fill<APP>(c, ring, 1u + t, t);
   }
   SuperAcc acc{0.0f, 0.0f, 0u, 0u, r};
+  // A very long row is posted for the CTA's idle warps, which take supergroups from the back.
+  const uint32_t end_super = ((nb + 3u) >> 2) - 1u;  // the last supergroup stays with this warp
+  bool posted = false;
+  if (MODE == kModeStripShared && nb > 4u * (kCoopMinSupers - 1u))
+    posted = coop_post(task, c.prim, c.sec, c.nq, c.head, c.tail, c.prev, c.prow, c.plen, c.want, c1, qlo, qhi,
+                       end_super, lane) != 0u;
+  // this warp stops in front of the supergroups the drawn tickets cover
+  auto taken = [&](uint32_t b) {
+    unsigned int k = 0;
+    if (lane == 0) k = ld_volatile(&task->ticket) & 0xFFFFu;
+    return (b >> 2) + __shfl_sync(0xFFFFFFFFu, k, 0) * kCoopChunkSupers >= end_super;
+  };
   absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
+  uint32_t b = 1;
   if (!ringed) {
 #pragma unroll 1
-    for (uint32_t b = 1; b < last_b; ++b)
+    for (; b < last_b; ++b) {
+      if (posted && (b & 3u) == 0u && taken(b)) break;
       absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, b, lane), b, false, true, lane, c1, qlo, qhi);
+    }
   } else {
     uint32_t t = 0;
     // Kept rolled on purpose: an unrolled sweep measured slower (instruction cache shared by
     // 40 warps that sit at different places of the kernel).
 #pragma unroll 1
-    for (uint32_t b = 1; b < last_b; ++b) {
+    for (; b < last_b; ++b) {
+      if (posted && (b & 3u) == 0u && taken(b)) {
+        // hand-over: the copies already in flight for b, b+1, .. are waited for and dropped
+        bool ok = true;
+        for (uint32_t i = 0; i < (uint32_t)kStages && b + i < last_b; ++i) {
+          const uint32_t st = (t + i) % (uint32_t)kStages;
+          ok = mbar_wait(ring.bar + 8u * st, (ring.parity >> st) & 1u) && ok;
+          ring.parity ^= 1u << st;
+        }
+        if (!__all_sync(0xFFFFFFFFu, ok)) { ring.failed = true; return 0xFFFFFFFFu; }
+        break;
+      }
       float A;
       if (!ring_sub<APP, CLEAN>(a, c, b, last_b, lane, ring, ring_ptr, t, A)) {
         ring.failed = true;
@@ -611,22 +853,51 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
       t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
     }
   }
+  uint32_t tickets = 0;
+  if (posted) {
+    tickets = coop_stop_tickets(task, lane);
+    if (b < last_b) {
+      // stopped early: the last supergroup (partial fill, row end) is still this warp's
+      acc.g = end_super / 3u;
+      acc.m = end_super - 3u * acc.g;
+      acc.r = fw::philox4x32_10(acc.g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+      if (APP == FW_APP_NODE2VEC && c.prev >= 0) {
+        // the chain of membership windows was cut by the helpers' part: restart it here
+        int32_t first = 0;
+        if (lane == 0) first = __ldg(reinterpret_cast<const int32_t*>(c.sec + (size_t)end_super * fw::kQuadsPerSuper));
+        first = __shfl_sync(0xFFFFFFFFu, first, 0);
+        c.from = warp_lower_bound(c.prow, 0u, c.plen, first, lane);
+      }
+#pragma unroll 1
+      for (b = 4u * end_super; b < last_b; ++b)
+        absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, b, lane), b, false, false, lane, c1, qlo, qhi);
+    }
+  }
   if (nb > 1u) absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, last_b, lane), last_b, true, false, lane, c1, qlo, qhi);
   warp_argmin(best.key, best.id);
-  if (best.id == 0xFFFFFFFFu) return best.id;
-
-  const uint32_t B = best.id;
+  uint32_t B = best.id;
+  if (posted) {
+    const unsigned long long own = ((unsigned long long)best.key << 32) | best.id;
+    const unsigned long long fin = coop_close(task, tickets, own, lane);
+    if (fin == kCoopFailed) { ring.failed = true; return 0xFFFFFFFFu; }
+    B = (uint32_t)fin;
+    if (B != 0xFFFFFFFFu && fin != own) {  // another warp reduced the winning strip
+      const unsigned long long pw = strip_redo<APP, CLEAN>(a, c, B, c1, qlo, qhi, lane);
+      return pick_in_row<APP, CLEAN>(a, c, B, (uint32_t)(pw >> 32), __uint_as_float((uint32_t)pw), lane);
+    }
+  }
+  if (B == 0xFFFFFFFFu) return B;
   return pick_in_row<APP, CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)),
                                  __shfl_sync(0xFFFFFFFFu, best.W, (int)(B & 31u)), lane);
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
-__global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_APP_NODE2VEC ? FW_MIN_BLOCKS : (MODE == FW_GROUP_STRIP ? FW_N2V_MIN_BLOCKS : 2)) walk_kernel(const __grid_constant__ WalkArgs a) {
+__global__ void __launch_bounds__(kThreads, MODE != FW_GROUP_EDGE && APP != FW_APP_NODE2VEC ? FW_MIN_BLOCKS : (MODE != FW_GROUP_EDGE ? FW_N2V_MIN_BLOCKS : 2)) walk_kernel(const __grid_constant__ WalkArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-  constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_STRIP && uses_ring<APP>() ? kStages * stage_bytes<APP>() : 0u;
+  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE && uses_ring<APP>() ? kStages * stage_bytes<APP>() : 0u;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
   Ring ring;
@@ -634,10 +905,15 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
   ring.bar = smem_addr(&s_bar[warp][0]);
   ring.parity = 0u;
   ring.failed = false;
-  if (MODE == FW_GROUP_STRIP && lane == 0) {
+  if (MODE != FW_GROUP_EDGE && lane == 0) {
 #pragma unroll
     for (int t = 0; t < kStages; ++t) mbar_init(ring.bar + 8u * t, 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __shared__ CoopTask s_task;  // the CTA's board for rows shared between its warps
+  if (threadIdx.x == 0) {
+    s_task.walking = kWarpsPerCta; s_task.lock = 0u; s_task.open = 0u; s_task.ticket = kCoopClosed;
+    s_task.epoch = 0u; s_task.done = 0u; s_task.end_super = 0u; s_task.best = ~0ull;
   }
   if (a.hist_in_smem)
     for (int z = threadIdx.x; z <= a.d; z += blockDim.x) s_hist[z] = 0u;
@@ -680,7 +956,7 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
           c.tail = (uint32_t)(e - 4 * q0);
           if (APP == FW_APP_METAPATH) c.want = a.schema[k % a.schema_len];
           c.from = 0u;
-          const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, (uint32_t)k, qlo, qhi, lane, ring, ring_ptr);
+          const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, (uint32_t)k, qlo, qhi, lane, ring, ring_ptr, &s_task);
           if (rel == 0xFFFFFFFFu) break;  // include/walker.cuh:1373-1374 (or a failed wait)
           const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
           if (nxt < 0 || (int64_t)nxt >= a.V) { status |= FW_STATUS_BAD_NEIGHBOR; break; }
@@ -702,6 +978,17 @@ __global__ void __launch_bounds__(kThreads, MODE == FW_GROUP_STRIP && APP != FW_
         if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
         else atomicAdd(a.scratch + kSlotHist + k, 1ull);
       }
+    }
+  }
+  // Out of queries: lend a hand to the rows the CTA's other warps post until all of them are done.
+  if (MODE == kModeStripShared) {
+    if (lane == 0) atomicSub(&s_task.walking, 1u);
+    for (uint32_t spin = 0; spin < (kCoopSpinLimit << 3) && !ring.failed; ++spin) {
+      unsigned int left = 0;
+      if (lane == 0) left = ld_volatile(&s_task.walking);
+      if (__shfl_sync(0xFFFFFFFFu, left, 0) == 0u) break;
+      if (!coop_help<APP, CLEAN>(a, &s_task, lane, ring, ring_ptr, &s_flags[warp][0])) ring.failed = true;
+      __nanosleep(256);
     }
   }
   if (ring.failed) {
@@ -732,19 +1019,20 @@ inline KernelFn pick_off(int xadj_bits) {
                          : (KernelFn)walk_kernel<APP, MODE, CLEAN, uint32_t>;
 }
 template <int APP>
-inline KernelFn pick_mode(int mode, bool clean, int xadj_bits) {
+inline KernelFn pick_mode(int mode, bool clean, bool shared, int xadj_bits) {
   if (mode == FW_GROUP_EDGE) return pick_off<APP, FW_GROUP_EDGE, false>(xadj_bits);
+  if (shared)
+    return clean ? pick_off<APP, kModeStripShared, true>(xadj_bits) : pick_off<APP, kModeStripShared, false>(xadj_bits);
   return clean ? pick_off<APP, FW_GROUP_STRIP, true>(xadj_bits) : pick_off<APP, FW_GROUP_STRIP, false>(xadj_bits);
 }
-// clean: all weights are known to be >= 0 and not NaN
-inline KernelFn pick_kernel(int app, int mode, bool clean, int xadj_bits) {
+// clean: all weights are known to be >= 0 and not NaN; shared: warps share very long rows
+inline KernelFn pick_kernel(int app, int mode, bool clean, bool shared, int xadj_bits) {
   switch (app) {
-    case FW_APP_DEEPWALK: return pick_mode<FW_APP_DEEPWALK>(mode, clean, xadj_bits);
-    case FW_APP_PPR: return pick_mode<FW_APP_PPR>(mode, clean, xadj_bits);
-    case FW_APP_NODE2VEC: return pick_mode<FW_APP_NODE2VEC>(mode, clean, xadj_bits);
+    case FW_APP_DEEPWALK: return pick_mode<FW_APP_DEEPWALK>(mode, clean, shared, xadj_bits);
+    case FW_APP_PPR: return pick_mode<FW_APP_PPR>(mode, clean, shared, xadj_bits);
+    case FW_APP_NODE2VEC: return pick_mode<FW_APP_NODE2VEC>(mode, clean, shared, xadj_bits);
     default:  // MetaPath biases are 0/1: nothing to clamp
-      return mode == FW_GROUP_EDGE ? pick_off<FW_APP_METAPATH, FW_GROUP_EDGE, false>(xadj_bits)
-                                   : pick_off<FW_APP_METAPATH, FW_GROUP_STRIP, true>(xadj_bits);
+      return pick_mode<FW_APP_METAPATH>(mode, true, shared, xadj_bits);
   }
 }
 

@@ -25,6 +25,10 @@
 
 using namespace fwk;
 
+// Graphs with a row of at least this many edges run the kernel variant whose warps share very
+// long rows (a single warp on a row of 10^6 edges is what the tail of a launch consists of).
+static constexpr int64_t kSharingAutoDegree = 262144;
+
 
 // ---------------------------------------------------------------------------
 // Engine
@@ -36,6 +40,8 @@ struct fw_engine {
   int64_t V = 0, E = 0;
   int xadj_bits = 32;
   bool clean_weights = false;  // every weight is >= 0 and not NaN: the kernels skip the clamp
+  int64_t max_degree = 0;
+  int sharing = -1;            // warps share very long rows: -1 by max degree, 0 never, 1 always
   void* d_xadj = nullptr;
   int32_t* d_adj = nullptr;
   float* d_weight = nullptr;
@@ -124,7 +130,11 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   a.schema_len = p->app == FW_APP_METAPATH ? p->schema_len : 1;
   for (int i = 0; i < kMaxSchema; ++i) a.schema[i] = (p->app == FW_APP_METAPATH && i < p->schema_len) ? p->schema[i] : 0;
   const int mode = p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode;
-  KernelFn fn = pick_kernel(p->app, mode, e->clean_weights, e->xadj_bits);
+  // measured: sharing halves DeepWalk's time on a graph with 10^6-edge hubs (2012 -> 974 ms) and
+  // costs node2vec 20 % there (its shared variant spills), so node2vec shares only on request
+  const bool shared = e->sharing > 0 ||
+                      (e->sharing < 0 && p->app != FW_APP_NODE2VEC && e->max_degree >= kSharingAutoDegree);
+  KernelFn fn = pick_kernel(p->app, mode, e->clean_weights, shared, e->xadj_bits);
   const size_t smem = kernel_smem_bytes(p->app, mode, p->d, a.hist_in_smem != 0);
   if (smem > 48 * 1024)
     FW_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -202,6 +212,8 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
   const bool want_l = which == 0 ? g->label != nullptr : (which & 2) != 0;
   int rc = FW_OK;
   auto body = [&]() -> int {
+    for (int64_t v = 0; v < g->V; ++v)
+      e->max_degree = std::max(e->max_degree, fw::row_begin(g, v + 1) - fw::row_begin(g, v));
     if (want_w && !g->weight) return fw::fail(FW_ERR_ARG, "graph has no weights");
     if (want_l && !g->label) return fw::fail(FW_ERR_ARG, "graph has no labels");
     const size_t xb = (size_t)(g->xadj_bits / 8) * (size_t)(g->V + 2);
@@ -238,6 +250,12 @@ extern "C" void fw_engine_destroy(fw_engine* e) {
   if (e->stream2) cudaStreamDestroy(e->stream2);
   for (auto& ev : e->ev) if (ev) cudaEventDestroy(ev);
   delete e;
+}
+
+extern "C" int fw_engine_set_sharing(fw_engine* e, int mode) {
+  if (!e || mode < -1 || mode > 1) return fw::fail(FW_ERR_ARG, "fw_engine_set_sharing: mode must be -1, 0 or 1");
+  e->sharing = mode;
+  return FW_OK;
 }
 
 extern "C" int fw_engine_device(const fw_engine* e, int* device, int* sm_count) {
@@ -512,7 +530,7 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
   for (int i = 0; i < kMaxSchema; ++i)
     a.schema[i] = (p->app == FW_APP_METAPATH && i < p->schema_len) ? p->schema[i] : 0;
   const int mode = p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode;
-  KernelFn fn = pick_kernel(p->app, mode, /*clean=*/false, xadj_bits);  // caller's weights: not inspected
+  KernelFn fn = pick_kernel(p->app, mode, /*clean=*/false, /*shared=*/false, xadj_bits);  // caller's arrays: not inspected
   const size_t smem = kernel_smem_bytes(p->app, mode, p->d, true);
   if (smem > 48 * 1024)
     FW_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -126,6 +126,12 @@ void fw_graph_destroy(fw_graph* g);
 int fw_engine_create(const fw_graph* g, int device, int which, fw_engine** out);
 void fw_engine_destroy(fw_engine* e);
 int fw_engine_device(const fw_engine* e, int* device, int* sm_count);
+/* Block-granularity sampling of very long rows (the role of sampler_block, include/sampler.cuh:87-127):
+ * warps that ran out of queries help the warps of their CTA that sit on rows of 32,768+ edges.
+ * mode -1 (default): on for DeepWalk, PPR and MetaPath on graphs whose largest out-degree is
+ * >= 262,144; 0: off; 1: on for every app.
+ * Results do not depend on it. */
+int fw_engine_set_sharing(fw_engine* e, int mode);
 
 /*
  * walk_test (include/walker.cuh:49-52, src/walk.cu:527-574): start points on

@@ -17,9 +17,10 @@ APPS = [
 MODES = [fw.GROUP_STRIP, fw.GROUP_EDGE]
 
 
-def run_both(arrs, app, kw, starts, mode, seed=1337, base=0):
+def run_both(arrs, app, kw, starts, mode, seed=1337, base=0, sharing=-1):
     g = fw.Graph.from_arrays(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"])
     eng = fw.Engine(g, 0)
+    eng.set_sharing(sharing)
     prm = fw.make_params(app, group_mode=mode, seed=seed, query_id_base=base, **kw)
     res, st, hist = eng.walk(prm, starts, want_hist=True)
     ref, steps, scanned, rhist = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], app,
@@ -66,6 +67,21 @@ def test_star_hub(app, kw, mode):
     kw = dict(kw)
     kw["d"] = 10
     assert_same(run_both(arrs, app, kw, starts, mode))
+
+
+@pytest.mark.parametrize("n", [3, 9, 64, 1000])
+@pytest.mark.parametrize("app,kw", APPS)
+def test_star_hub_shared_between_warps(app, kw, n):
+    """Rows of 100,000 edges with the block-granularity path forced on: warps that are out of
+    queries take supergroups from the back of a posted row; the walks must not change.  With 3 or
+    9 queries most warps of the CTA are idle from the start, with 1000 they become idle at the end."""
+    arrs = graphs.star()
+    arrs["label"][:100000] = np.arange(100000) % 5
+    starts = np.zeros(n, dtype=np.int32)
+    starts[1::2] = np.arange(1, n, 2) % 1000 + 1   # leaves lead straight back to the hub
+    kw = dict(kw)
+    kw["d"] = min(kw["d"], 10)
+    assert_same(run_both(arrs, app, kw, starts, fw.GROUP_STRIP, seed=5, sharing=1))
 
 
 @pytest.mark.parametrize("app,kw", APPS)
