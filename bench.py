@@ -10,7 +10,8 @@ range (walk round r of a walks-per-vertex = N job), so per-GPU work is fixed
 carries the barrier and the final reduction of counters and times.
 
 Prints ONE JSON line (rank 0).  `value` is walk steps per second with inputs
-resident in HBM; `e2e` is the same through fw_walk with pinned host buffers.
+resident in HBM; `e2e` is the same through fw_walk_batch_into with pinned host buffers
+(start vertices copied in, the whole walk table copied out, four double-buffered batches).
 """
 import argparse
 import ctypes
@@ -271,7 +272,9 @@ def main():
         prm = fw.make_params(APPS[args.app], seed=1337, query_id_base=(rank + world * step_idx) * n, **kw)
         if host:
             st = fw.WalkStats()
-            rc = fw.lib().fw_walk(eng._h, prm[0], starts_host.data_ptr(), n, result_host.data_ptr(), st, None)
+            # four double-buffered batches: the result of one travels to the host while the next walks
+            rc = fw.lib().fw_walk_batch_into(eng._h, prm[0], starts_host.data_ptr(), n, (n + 3) // 4, 512,
+                                             result_host.data_ptr(), st, None)
             if rc:
                 raise RuntimeError(fw.lib().fw_last_error())
             return st

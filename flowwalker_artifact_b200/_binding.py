@@ -77,6 +77,8 @@ def lib():
         L.fw_walk.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, ctypes.POINTER(WalkStats), vp]
         L.fw_walk_batch.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, i64, i32,
                                     ctypes.POINTER(vp), ctypes.POINTER(WalkStats), vp]
+        L.fw_walk_batch_into.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, i64, i32, vp,
+                                         ctypes.POINTER(WalkStats), vp]
         L.fw_free_pinned.argtypes = [vp]
         L.fw_free_pinned.restype = None
         _lib = L

@@ -319,15 +319,12 @@ extern "C" void fw_free_pinned(void* p) {
   if (p) cudaFreeHost(p);
 }
 
-// walk_batch: two streams, double-buffered batches (src/walk.cu:373-466).
-extern "C" int fw_walk_batch(fw_engine* e, const fw_walk_params* p, const int32_t* starts_host,
-                             int64_t n, int64_t batch_size, int32_t headroom_mb,
-                             int32_t** result_pinned, fw_walk_stats* stats, uint64_t* len_hist) {
-  fw::clear_error();
-  int rc = check_params(e, p, n);
-  if (rc) return rc;
-  if (!result_pinned || (n > 0 && !starts_host)) return fw::fail(FW_ERR_ARG, "null buffer");
-  *result_pinned = nullptr;
+// Two streams, double-buffered batches (src/walk.cu:373-466): batch i+1 walks while the result of
+// batch i travels to `pinned` (host memory of n*(d+1) cells, ideally page-locked).
+static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* starts_host, int64_t n,
+                        int64_t batch_size, int32_t headroom_mb, int32_t* pinned, fw_walk_stats* stats,
+                        uint64_t* len_hist) {
+  int rc = FW_OK;
   DeviceGuard guard(e->device);
   const size_t D = (size_t)p->d + 1;
   if (batch_size <= 0) {  // --autobatch, src/main.cu:259-271
@@ -344,12 +341,7 @@ extern "C" int fw_walk_batch(fw_engine* e, const fw_walk_params* p, const int32_
   const size_t words = (size_t)kSlotHist + D;
   rc = ensure_scratch(e, (int)(2 * words));
   if (rc) return rc;
-  int32_t* pinned = nullptr;
-  {
-    cudaError_t err = cudaMallocHost(&pinned, std::max<size_t>((size_t)n * D * 4, 4));
-    if (err != cudaSuccess) return fw::fail(FW_ERR_NOMEM, "cudaMallocHost failed: %s", cudaGetErrorString(err));
-  }
-  auto bail = [&](int code) { cudaStreamSynchronize(e->stream); cudaStreamSynchronize(e->stream2); cudaFreeHost(pinned); return code; };
+  auto bail = [&](int code) { cudaStreamSynchronize(e->stream); cudaStreamSynchronize(e->stream2); return code; };
   for (int i = 0; i < 2; ++i) {
     rc = ensure_cap(&e->d_starts[i], &e->cap_starts[i], (size_t)batch_size);
     if (!rc) rc = ensure_cap(&e->d_result[i], &e->cap_result[i], (size_t)batch_size * D);
@@ -402,8 +394,37 @@ extern "C" int fw_walk_batch(fw_engine* e, const fw_walk_params* p, const int32_
   }
   cudaEventDestroy(t0); cudaEventDestroy(t1);
   if (rc) return bail(rc);
+  return FW_OK;
+}
+
+// walk_batch (include/walker.cuh:54-57, src/walk.cu:576-649): the callee allocates the pinned result.
+extern "C" int fw_walk_batch(fw_engine* e, const fw_walk_params* p, const int32_t* starts_host,
+                             int64_t n, int64_t batch_size, int32_t headroom_mb,
+                             int32_t** result_pinned, fw_walk_stats* stats, uint64_t* len_hist) {
+  fw::clear_error();
+  int rc = check_params(e, p, n);
+  if (rc) return rc;
+  if (!result_pinned || (n > 0 && !starts_host)) return fw::fail(FW_ERR_ARG, "null buffer");
+  *result_pinned = nullptr;
+  DeviceGuard guard(e->device);
+  int32_t* pinned = nullptr;
+  cudaError_t err = cudaMallocHost(&pinned, std::max<size_t>((size_t)n * ((size_t)p->d + 1) * 4, 4));
+  if (err != cudaSuccess) return fw::fail(FW_ERR_NOMEM, "cudaMallocHost failed: %s", cudaGetErrorString(err));
+  rc = walk_batches(e, p, starts_host, n, batch_size, headroom_mb, pinned, stats, len_hist);
+  if (rc) { cudaFreeHost(pinned); return rc; }
   *result_pinned = pinned;
   return FW_OK;
+}
+
+// Same pipeline into a buffer the caller owns (page-locked memory lets the copies overlap the walks).
+extern "C" int fw_walk_batch_into(fw_engine* e, const fw_walk_params* p, const int32_t* starts_host,
+                                  int64_t n, int64_t batch_size, int32_t headroom_mb,
+                                  int32_t* result_host, fw_walk_stats* stats, uint64_t* len_hist) {
+  fw::clear_error();
+  int rc = check_params(e, p, n);
+  if (rc) return rc;
+  if (n > 0 && (!starts_host || !result_host)) return fw::fail(FW_ERR_ARG, "null buffer");
+  return walk_batches(e, p, starts_host, n, batch_size, headroom_mb, result_host, stats, len_hist);
 }
 
 // ---------------------------------------------------------------------------

@@ -166,6 +166,12 @@ int fw_walk_batch(fw_engine* e, const fw_walk_params* params, const int32_t* sta
                   int64_t n, int64_t batch_size, int32_t headroom_mb,
                   int32_t** result_pinned, fw_walk_stats* stats, uint64_t* len_hist);
 void fw_free_pinned(void* p);
+/* The same double-buffered pipeline into a host buffer the caller owns (int32[n*(d+1)]; page-locked
+ * memory lets the device-to-host copy of one batch overlap the walk of the next).  Stands in for
+ * timing_batch_async (src/walk.cu:373-466) without its allocation. */
+int fw_walk_batch_into(fw_engine* e, const fw_walk_params* params, const int32_t* starts_host,
+                       int64_t n, int64_t batch_size, int32_t headroom_mb,
+                       int32_t* result_host, fw_walk_stats* stats, uint64_t* len_hist);
 
 /*
  * Failure-detection self-test, no counterpart in the reference (whose device waits are

@@ -124,6 +124,11 @@ def test_shards_union_equals_single_run():
     assert (np.vstack([a, b]) == full).all()
     out, st = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=128)
     assert (out == full).all() and st.launches == 8
+    into = np.full((1000, 41), -9, dtype=np.int32)
+    st2 = fw.WalkStats()
+    prm = fw.make_params(fw.APP_DEEPWALK, d=40)
+    rc = fw.lib().fw_walk_batch_into(eng._h, prm[0], starts.ctypes.data, 1000, 300, 512, into.ctypes.data, st2, None)
+    assert rc == 0 and (into == full).all() and st2.launches == 4 and st2.steps == st.steps
     eng.close()
 
 
