@@ -85,3 +85,25 @@ def test_cli_batches_and_printresult(tmp_path):
     r = run("--input", prefix, "--ppr", "--n", "50", "--save_result", out)
     assert r.returncode == 0
     assert (np.fromfile(out, dtype=np.int32).reshape(50, 81)[:, 0] == g.max_degree()[0]).all()
+
+
+@pytest.mark.gpu
+def test_cli_two_gpus_and_int64_offsets(tmp_path):
+    """Queries sharded over two devices reproduce the single-device table; 64-bit offset files load."""
+    import ctypes
+    n_dev = ctypes.c_int(0)
+    fw.lib().fw_device_count(ctypes.byref(n_dev))
+    g = fw.rmat(12, 16 << 12, weight_range=(0.0, 1.0), n_labels=5, xadj_bits=64)
+    prefix = str(tmp_path / "g64")
+    g.save(prefix)
+    out1 = str(tmp_path / "w1.bin")
+    r = run("--input", prefix, "--deepwalk", "--all", "--d", "12", "--save_result", out1)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ref = O.graph_walk(g, fw.APP_DEEPWALK, np.arange(g.V, dtype=np.int32), d=12)[0]
+    assert (np.fromfile(out1, dtype=np.int32).reshape(g.V, 13) == ref).all()
+    if n_dev.value < 2:
+        pytest.skip("one visible device: the two-device half of this test needs two")
+    out2 = str(tmp_path / "w2.bin")
+    r = run("--input", prefix, "--deepwalk", "--all", "--d", "12", "--gpus", "2", "--save_result", out2)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert (np.fromfile(out2, dtype=np.int32).reshape(g.V, 13) == ref).all()

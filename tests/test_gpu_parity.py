@@ -124,6 +124,8 @@ def test_shards_union_equals_single_run():
     assert (np.vstack([a, b]) == full).all()
     out, st = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=128)
     assert (out == full).all() and st.launches == 8
+    auto, st_auto = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=0)  # autobatch
+    assert (auto == full).all() and st_auto.launches == 1
     into = np.full((1000, 41), -9, dtype=np.int32)
     st2 = fw.WalkStats()
     prm = fw.make_params(fw.APP_DEEPWALK, d=40)
