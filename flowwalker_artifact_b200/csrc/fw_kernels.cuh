@@ -63,6 +63,7 @@ struct WalkArgs {
   int32_t d;
   uint32_t tp_thresh;
   float inv_p, inv_q;
+  float n2v_fmax;  // node2vec: max(1, 1/p, 1/q) with a margin of 1e-5 for rounding
   uint32_t k0, k1;
   int32_t hist_in_smem;
   int32_t schema_len;
@@ -733,6 +734,144 @@ __device__ __noinline__ unsigned long long strip_redo(const WalkArgs& args, Step
   return ((unsigned long long)pick << 32) | __float_as_uint(W);
 }
 
+// ---- node2vec: sweep with the membership test only where it can matter ----
+//
+// bias = w * f with f in {1/p, 1, 1/q}, so a strip's total bias W is at most fmax * sum(w) and
+// its key E / W at least E / (fmax * sum(w)).  The sweep therefore adds up the plain weights
+// only (no neighbour ids, no membership test) and looks closer only at strips whose optimistic
+// key could still beat the warp's best so far: a handful per row once the first supergroup has
+// set a bound.  A strip that is skipped has a true key above the final minimum, so the result is
+// the one the full evaluation gives.  The reference evaluates the membership test for every
+// candidate of every row (include/app.cuh:109-122).
+
+// Exact biases of strip (s, L) spread over the warp: lane t holds edges 2*(t&1), 2*(t&1)+1 of the
+// strip's quad t>>1, i.e. the strip's 64 edges in canonical order are lane 0 (b0, b1), lane 1
+// (b0, b1), ...  Membership by one binary search over prev's row per edge (two per lane, run side
+// by side).  Returns the strip's total in the canonical summation order, identical on all lanes.
+template <bool CLEAN>
+__device__ __forceinline__ float n2v_strip_exact(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t L,
+                                                 uint32_t lane, float& b0, float& b1) {
+  const uint32_t q = s * fw::kQuadsPerSuper + 32u * (lane >> 1) + L;
+  const uint32_t k0 = 2u * (lane & 1u);
+  b0 = 0.0f;
+  b1 = 0.0f;
+  int32_t x0 = 0, x1 = 0;
+  const uint32_t r0 = 4u * q + k0;
+  const bool v0 = q < c.nq && r0 >= c.head && r0 < c.tail;
+  const bool v1 = q < c.nq && r0 + 1u >= c.head && r0 + 1u < c.tail;
+  if (q < c.nq) {
+    // the lane's two edges are the low or the high half of the quad: one 8-byte load each
+    const float2 w = __ldg(reinterpret_cast<const float2*>(c.prim + q) + (lane & 1u));
+    const int2 x = __ldg(reinterpret_cast<const int2*>(c.sec + q) + (lane & 1u));
+    b0 = w.x; b1 = w.y; x0 = x.x; x1 = x.y;
+  }
+  // lower bounds of x0 and x1 in prev's row, both searches advancing together
+  uint32_t lo0 = 0, hi0 = v0 && x0 != c.prev ? c.plen : 0u;
+  uint32_t lo1 = 0, hi1 = v1 && x1 != c.prev ? c.plen : 0u;
+  while (lo0 < hi0 || lo1 < hi1) {
+    const uint32_t m0 = lo0 + ((hi0 - lo0) >> 1), m1 = lo1 + ((hi1 - lo1) >> 1);
+    const int32_t p0 = lo0 < hi0 ? __ldg(c.prow + m0) : 0;
+    const int32_t p1 = lo1 < hi1 ? __ldg(c.prow + m1) : 0;
+    if (lo0 < hi0) { if (p0 < x0) lo0 = m0 + 1u; else hi0 = m0; }
+    if (lo1 < hi1) { if (p1 < x1) lo1 = m1 + 1u; else hi1 = m1; }
+  }
+  const bool linked0 = v0 && x0 != c.prev && lo0 < c.plen && __ldg(c.prow + lo0) == x0;
+  const bool linked1 = v1 && x1 != c.prev && lo1 < c.plen && __ldg(c.prow + lo1) == x1;
+  b0 = !v0 ? 0.0f : x0 == c.prev ? __fmul_rn(b0, a.inv_p) : linked0 ? b0 : __fmul_rn(b0, a.inv_q);
+  b1 = !v1 ? 0.0f : x1 == c.prev ? __fmul_rn(b1, a.inv_p) : linked1 ? b1 : __fmul_rn(b1, a.inv_q);
+  if (!CLEAN) { b0 = pos(b0); b1 = pos(b1); }
+  // (w0+w1)+(w2+w3) per quad, (S0+S1)+(S2+S3) per sub-block, (A0+A1)+(A2+A3): a butterfly
+  float t = __fadd_rn(b0, b1);
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float o = __shfl_xor_sync(0xFFFFFFFFu, t, d);
+    t = (lane & d) ? __fadd_rn(o, t) : __fadd_rn(t, o);  // same operands in the same order on both lanes
+  }
+  return t;
+}
+
+constexpr int kN2vDenseLanes = 6;  // more passing strips than this in a supergroup: evaluate it block-wise
+
+// One weighted pick for node2vec from the second step on (c.prev >= 0), rows of more than 32 quads.
+// `r` is the lane's Philox block 0.  Returns the edge index relative to quad 0 or 0xFFFFFFFF.
+template <bool CLEAN>
+__device__ __forceinline__ uint32_t sample_row_n2v(const WalkArgs& a, const StepCtx& c, fw::Philox4 r, uint32_t c1,
+                                                   uint32_t qlo, uint32_t qhi, uint32_t lane) {
+  const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
+  const uint32_t last_b = nb - 1u;
+  const uint32_t nsuper = (nb + 3u) >> 2;
+  Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
+  uint32_t g = 0, m = 0;
+#pragma unroll 1
+  for (uint32_t s = 0; s < nsuper; ++s) {
+    // plain weights of the lane's strip: an upper bound of its total bias after scaling by fmax
+    float A[4];
+#pragma unroll
+    for (uint32_t i = 0; i < 4u; ++i) {
+      const uint32_t b = 4u * s + i;
+      A[i] = b <= last_b ? sub_global<FW_APP_DEEPWALK, CLEAN>(a, c, b, lane) : 0.0f;  // warp-uniform test
+    }
+    const float Wplain = __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3]));
+    const uint32_t x = m == 0u ? r.x : m == 1u ? r.y : r.z;
+    const float bound = __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key));
+    const int z = __clz((int)x);
+    const float lower = z ? (float)z : __fmul_rn((float)(x << 1), 0.72f * 0x1p-32f);
+    const bool pass = Wplain > 0.0f &&
+                      !(lower > __fmul_rn(__fmul_rn(bound, __fmul_rn(Wplain, a.n2v_fmax)), 1.000001f));
+    uint32_t mask = __ballot_sync(0xFFFFFFFFu, pass);
+    if (__popc(mask) > kN2vDenseLanes) {
+      // many candidates (the first supergroups of a row): the block-wise membership test does all
+      // strips of the supergroup at once; its chain of windows starts at this supergroup
+      c.from = 0u;
+      if (s > 0u) {
+        int32_t first = 0;
+        if (lane == 0) first = __ldg(reinterpret_cast<const int32_t*>(c.sec + (size_t)s * fw::kQuadsPerSuper));
+        first = __shfl_sync(0xFFFFFFFFu, first, 0);
+        c.from = warp_lower_bound(c.prow, 0u, c.plen, first, lane);
+      }
+#pragma unroll 1
+      for (uint32_t i = 0; i < 4u; ++i) {
+        const uint32_t b = 4u * s + i;
+        A[i] = b <= last_b ? sub_global<FW_APP_NODE2VEC, CLEAN>(a, c, b, lane) : 0.0f;
+      }
+      offer(best, x, r.w, __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3])), s * 32u + lane);
+    } else {
+      while (mask) {
+        const uint32_t L = (uint32_t)__ffs((int)mask) - 1u;
+        mask &= mask - 1u;
+        float b0, b1;
+        const float W = n2v_strip_exact<CLEAN>(a, c, s, L, lane, b0, b1);
+        if (lane == L) offer(best, x, r.w, W, s * 32u + lane);
+      }
+    }
+    if (++m == 3u) { m = 0u; r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
+  }
+  warp_argmin(best.key, best.id);
+  const uint32_t B = best.id;
+  if (B == 0xFFFFFFFFu) return B;
+  // pick inside the winning strip: its exact biases again, spread over the warp in canonical order
+  const uint32_t sB = B >> 5, lB = B & 31u;
+  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)lB);
+  float b0, b1;
+  const float W = n2v_strip_exact<CLEAN>(a, c, sB, lB, lane, b0, b1);
+  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
+  float acc = 0.0f;
+  uint32_t cnt = 0;
+#pragma unroll 1
+  for (int t = 0; t < 32; ++t) {
+    acc = __fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, b0, t)); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, b1, t)); cnt += acc <= thr ? 1u : 0u;
+    if (cnt < 2u * (uint32_t)(t + 1)) break;  // found (warp-uniform)
+  }
+  if (cnt >= 64u) {  // rounding pushed u * W past the sequential total: the strip's last positive edge
+    const uint32_t m1 = __ballot_sync(0xFFFFFFFFu, b1 > 0.0f), m0 = __ballot_sync(0xFFFFFFFFu, b0 > 0.0f);
+    const int t1 = 31 - __clz((int)m1), t0 = 31 - __clz((int)m0);  // -1 when the mask is empty
+    cnt = t1 >= t0 ? 2u * (uint32_t)t1 + 1u : 2u * (uint32_t)t0;
+  }
+  // position z = 4 j + k of the strip: quad 512 s + 32 j + l, edge k
+  return 4u * (sB * fw::kQuadsPerSuper + 32u * (cnt >> 2) + lB) + (cnt & 3u);
+}
+
 // One weighted pick in the row described by c, by one warp.  Returns the
 // edge index relative to quad 0 of the row, or 0xFFFFFFFF when no edge has
 // positive bias.
@@ -798,6 +937,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   // global memory (boundary quads, partial fill), the interior ones through the ring when
   // there are any.  Four sub-blocks make a supergroup; a lane's four partial sums A0..A3 are
   // combined as (A0+A1)+(A2+A3) and tested once per supergroup.
+  if (APP == FW_APP_NODE2VEC && c.prev >= 0) return sample_row_n2v<CLEAN>(a, c, r, c1, qlo, qhi, lane);
   const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
   const uint32_t last_b = nb - 1u;
   const bool ringed = uses_ring<APP>() && nb >= 3u;
