@@ -739,9 +739,8 @@ __device__ __noinline__ unsigned long long strip_redo(const WalkArgs& args, Step
 // bias = w * f with f in {1/p, 1, 1/q}, so a strip's total bias W is at most fmax * sum(w) and
 // its key E / W at least E / (fmax * sum(w)).  The sweep therefore adds up the plain weights
 // only (no neighbour ids, no membership test) and looks closer only at strips whose optimistic
-// key could still beat the warp's best so far: a handful per row once the first supergroup has
-// set a bound.  A strip that is skipped has a true key above the final minimum, so the result is
-// the one the full evaluation gives.  The reference evaluates the membership test for every
+// key could still beat the best true key so far: a handful per row.  A strip that is skipped has
+// a true key above the final minimum, so the result is the one the full evaluation gives.  The reference evaluates the membership test for every
 // candidate of every row (include/app.cuh:109-122).
 
 // Exact biases of strip (s, L) spread over the warp: lane t holds edges 2*(t&1), 2*(t&1)+1 of the
@@ -790,21 +789,23 @@ __device__ __forceinline__ float n2v_strip_exact(const WalkArgs& a, const StepCt
   return t;
 }
 
-constexpr int kN2vDenseLanes = 6;  // more passing strips than this in a supergroup: evaluate it block-wise
-
 // One weighted pick for node2vec from the second step on (c.prev >= 0), rows of more than 32 quads.
 // `r` is the lane's Philox block 0.  Returns the edge index relative to quad 0 or 0xFFFFFFFF.
+//
+// Per supergroup every lane forms the optimistic key of its strip, E / (fmax * sum of plain
+// weights), which is never above the strip's true key.  Strips are then evaluated exactly in the
+// order of their optimistic keys, and only while that key does not exceed the best true key found
+// so far: usually one or two strips in the first supergroup of a row and none in the others.
 template <bool CLEAN>
 __device__ __forceinline__ uint32_t sample_row_n2v(const WalkArgs& a, const StepCtx& c, fw::Philox4 r, uint32_t c1,
                                                    uint32_t qlo, uint32_t qhi, uint32_t lane) {
   const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
   const uint32_t last_b = nb - 1u;
   const uint32_t nsuper = (nb + 3u) >> 2;
-  Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
+  uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu, best_pick = 0u;  // warp-uniform
   uint32_t g = 0, m = 0;
 #pragma unroll 1
   for (uint32_t s = 0; s < nsuper; ++s) {
-    // plain weights of the lane's strip: an upper bound of its total bias after scaling by fmax
     float A[4];
 #pragma unroll
     for (uint32_t i = 0; i < 4u; ++i) {
@@ -813,48 +814,33 @@ __device__ __forceinline__ uint32_t sample_row_n2v(const WalkArgs& a, const Step
     }
     const float Wplain = __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3]));
     const uint32_t x = m == 0u ? r.x : m == 1u ? r.y : r.z;
-    const float bound = __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key));
-    const int z = __clz((int)x);
-    const float lower = z ? (float)z : __fmul_rn((float)(x << 1), 0.72f * 0x1p-32f);
-    const bool pass = Wplain > 0.0f &&
-                      !(lower > __fmul_rn(__fmul_rn(bound, __fmul_rn(Wplain, a.n2v_fmax)), 1.000001f));
-    uint32_t mask = __ballot_sync(0xFFFFFFFFu, pass);
-    if (__popc(mask) > kN2vDenseLanes) {
-      // many candidates (the first supergroups of a row): the block-wise membership test does all
-      // strips of the supergroup at once; its chain of windows starts at this supergroup
-      c.from = 0u;
-      if (s > 0u) {
-        int32_t first = 0;
-        if (lane == 0) first = __ldg(reinterpret_cast<const int32_t*>(c.sec + (size_t)s * fw::kQuadsPerSuper));
-        first = __shfl_sync(0xFFFFFFFFu, first, 0);
-        c.from = warp_lower_bound(c.prow, 0u, c.plen, first, lane);
-      }
+    // optimistic key bits; 0xFFFFFFFF = nothing to evaluate in this lane
+    uint32_t klo = 0xFFFFFFFFu;
+    if (Wplain > 0.0f) klo = __float_as_uint(__fdiv_rn(fw::exp_key(x), __fmul_rn(Wplain, a.n2v_fmax)));
 #pragma unroll 1
-      for (uint32_t i = 0; i < 4u; ++i) {
-        const uint32_t b = 4u * s + i;
-        A[i] = b <= last_b ? sub_global<FW_APP_NODE2VEC, CLEAN>(a, c, b, lane) : 0.0f;
+    for (;;) {
+      const uint32_t kmin = __reduce_min_sync(0xFFFFFFFFu, klo);
+      if (kmin == 0xFFFFFFFFu || kmin > best_key) break;  // equal keys still need a look: the lower id wins
+      const uint32_t L = (uint32_t)__ffs((int)__ballot_sync(0xFFFFFFFFu, klo == kmin)) - 1u;
+      float b0, b1;
+      const float W = n2v_strip_exact<CLEAN>(a, c, s, L, lane, b0, b1);
+      const uint32_t xL = __shfl_sync(0xFFFFFFFFu, x, (int)L), pL = __shfl_sync(0xFFFFFFFFu, r.w, (int)L);
+      if (W > 0.0f) {
+        const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(xL), W));
+        const uint32_t id = s * 32u + L;
+        if (bits < best_key || (bits == best_key && id < best_id)) { best_key = bits; best_id = id; best_pick = pL; }
       }
-      offer(best, x, r.w, __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3])), s * 32u + lane);
-    } else {
-      while (mask) {
-        const uint32_t L = (uint32_t)__ffs((int)mask) - 1u;
-        mask &= mask - 1u;
-        float b0, b1;
-        const float W = n2v_strip_exact<CLEAN>(a, c, s, L, lane, b0, b1);
-        if (lane == L) offer(best, x, r.w, W, s * 32u + lane);
-      }
+      if (lane == L) klo = 0xFFFFFFFFu;  // evaluated
     }
     if (++m == 3u) { m = 0u; r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
   }
-  warp_argmin(best.key, best.id);
-  const uint32_t B = best.id;
+  const uint32_t B = best_id;
   if (B == 0xFFFFFFFFu) return B;
   // pick inside the winning strip: its exact biases again, spread over the warp in canonical order
   const uint32_t sB = B >> 5, lB = B & 31u;
-  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)lB);
   float b0, b1;
   const float W = n2v_strip_exact<CLEAN>(a, c, sB, lB, lane, b0, b1);
-  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
+  const float thr = __fmul_rn((float)(best_pick >> 8) * 0x1p-24f, W);
   float acc = 0.0f;
   uint32_t cnt = 0;
 #pragma unroll 1
