@@ -27,12 +27,6 @@ constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared
 #ifndef FW_STAGES
 #define FW_STAGES 2
 #endif
-// node2vec sweeps long rows with direct loads: its time goes into the membership test, whose
-// dependent loads are hidden by resident warps, and without the ring's 8 KB per warp four CTAs
-// fit on an SM instead of three (measured 377 ms vs 518 ms on an R-MAT scale-20 graph).
-#ifndef FW_N2V_RING
-#define FW_N2V_RING 0
-#endif
 #ifndef FW_N2V_MIN_BLOCKS
 #define FW_N2V_MIN_BLOCKS 4
 #endif
@@ -41,9 +35,9 @@ constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared
 #endif
 constexpr int kStages = FW_STAGES;       // ring depth per warp
 constexpr uint32_t kSubBytes = 16u * fw::kQuadsPerSub;  // 2 KB: one ring stage, one bulk copy
-// whether an app sweeps long rows through the shared-memory ring
+// every app sweeps long rows through the shared-memory ring (node2vec's sweep reads plain weights)
 template <int APP>
-__host__ __device__ constexpr bool uses_ring() { return APP != FW_APP_NODE2VEC || FW_N2V_RING != 0; }
+__host__ __device__ constexpr bool uses_ring() { return true; }
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls of an mbarrier before giving up
 
 // Scratch words (uint64) in device memory.
@@ -379,7 +373,7 @@ struct Ring {
 
 template <int APP>
 __device__ __forceinline__ constexpr uint32_t stage_bytes() {
-  return APP == FW_APP_NODE2VEC ? 2u * kSubBytes : kSubBytes;
+  return kSubBytes;
 }
 
 // Issues the bulk copies of sub-block b into stage T (lane 0 only calls this).
@@ -389,7 +383,6 @@ __device__ __forceinline__ void ring_fill(const StepCtx& c, const Ring& ring, ui
   const uint32_t bar = ring.bar + 8u * T;
   mbar_expect_tx(bar, kSB);
   bulk_g2s(ring.data + T * kSB, c.prim + (size_t)b * fw::kQuadsPerSub, kSubBytes, bar);
-  if (APP == FW_APP_NODE2VEC) bulk_g2s(ring.data + T * kSB + kSubBytes, c.sec + (size_t)b * fw::kQuadsPerSub, kSubBytes, bar);
 }
 
 // One interior sub-block b from stage T of the ring: wait for its copy, reduce the lane's
@@ -426,6 +419,120 @@ __device__ __forceinline__ bool ring_sub(const WalkArgs& a, const StepCtx& c, ui
   return true;
 }
 
+// ---- node2vec: sweep with the membership test only where it can matter ----
+//
+// bias = w * f with f in {1/p, 1, 1/q}, so a strip's total bias W is at most fmax * sum(w) and
+// its key E / W at least E / (fmax * sum(w)).  The sweep therefore adds up the plain weights
+// only (no neighbour ids, no membership test) and looks closer only at strips whose optimistic
+// key could still beat the best true key so far: a handful per row.  A strip that is skipped has
+// a true key above the final minimum, so the result is the one the full evaluation gives.  The reference evaluates the membership test for every
+// candidate of every row (include/app.cuh:109-122).
+
+// Exact biases of strip (s, L) spread over the warp: lane t holds edges 2*(t&1), 2*(t&1)+1 of the
+// strip's quad t>>1, i.e. the strip's 64 edges in canonical order are lane 0 (b0, b1), lane 1
+// (b0, b1), ...  Membership by one binary search over prev's row per edge (two per lane, run side
+// by side).  Returns the strip's total in the canonical summation order, identical on all lanes.
+template <bool CLEAN>
+__device__ __forceinline__ float n2v_strip_exact(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t L,
+                                                 uint32_t lane, float& b0, float& b1) {
+  const uint32_t q = s * fw::kQuadsPerSuper + 32u * (lane >> 1) + L;
+  const uint32_t k0 = 2u * (lane & 1u);
+  b0 = 0.0f;
+  b1 = 0.0f;
+  int32_t x0 = 0, x1 = 0;
+  const uint32_t r0 = 4u * q + k0;
+  const bool v0 = q < c.nq && r0 >= c.head && r0 < c.tail;
+  const bool v1 = q < c.nq && r0 + 1u >= c.head && r0 + 1u < c.tail;
+  if (q < c.nq) {
+    // the lane's two edges are the low or the high half of the quad: one 8-byte load each
+    const float2 w = __ldg(reinterpret_cast<const float2*>(c.prim + q) + (lane & 1u));
+    const int2 x = __ldg(reinterpret_cast<const int2*>(c.sec + q) + (lane & 1u));
+    b0 = w.x; b1 = w.y; x0 = x.x; x1 = x.y;
+  }
+  // lower bounds of x0 and x1 in prev's row, both searches advancing together
+  uint32_t lo0 = 0, hi0 = v0 && x0 != c.prev ? c.plen : 0u;
+  uint32_t lo1 = 0, hi1 = v1 && x1 != c.prev ? c.plen : 0u;
+  while (lo0 < hi0 || lo1 < hi1) {
+    const uint32_t m0 = lo0 + ((hi0 - lo0) >> 1), m1 = lo1 + ((hi1 - lo1) >> 1);
+    const int32_t p0 = lo0 < hi0 ? __ldg(c.prow + m0) : 0;
+    const int32_t p1 = lo1 < hi1 ? __ldg(c.prow + m1) : 0;
+    if (lo0 < hi0) { if (p0 < x0) lo0 = m0 + 1u; else hi0 = m0; }
+    if (lo1 < hi1) { if (p1 < x1) lo1 = m1 + 1u; else hi1 = m1; }
+  }
+  const bool linked0 = v0 && x0 != c.prev && lo0 < c.plen && __ldg(c.prow + lo0) == x0;
+  const bool linked1 = v1 && x1 != c.prev && lo1 < c.plen && __ldg(c.prow + lo1) == x1;
+  b0 = !v0 ? 0.0f : x0 == c.prev ? __fmul_rn(b0, a.inv_p) : linked0 ? b0 : __fmul_rn(b0, a.inv_q);
+  b1 = !v1 ? 0.0f : x1 == c.prev ? __fmul_rn(b1, a.inv_p) : linked1 ? b1 : __fmul_rn(b1, a.inv_q);
+  if (!CLEAN) { b0 = pos(b0); b1 = pos(b1); }
+  // (w0+w1)+(w2+w3) per quad, (S0+S1)+(S2+S3) per sub-block, (A0+A1)+(A2+A3): a butterfly
+  float t = __fadd_rn(b0, b1);
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float o = __shfl_xor_sync(0xFFFFFFFFu, t, d);
+    t = (lane & d) ? __fadd_rn(o, t) : __fadd_rn(t, o);  // same operands in the same order on both lanes
+  }
+  return t;
+}
+
+// node2vec, end of a supergroup: every lane holds the plain-weight total of its strip (Wplain) and
+// its random word x (pick word pw).  Each lane forms the optimistic key of its strip,
+// E / (fmax * Wplain), which is never above the strip's true key; strips are then evaluated
+// exactly in the order of their optimistic keys and only while that key does not exceed the best
+// true key so far: usually one or two strips in the first supergroup of a row, none in the others.
+// `best` is kept identical on all lanes.
+template <bool CLEAN>
+__device__ __forceinline__ void n2v_test(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t lane,
+                                         float Wplain, uint32_t x, uint32_t pw, Best& best) {
+  uint32_t klo = 0xFFFFFFFFu;  // optimistic key bits; 0xFFFFFFFF = nothing to evaluate in this lane
+  if (Wplain > 0.0f) klo = __float_as_uint(__fdiv_rn(fw::exp_key(x), __fmul_rn(Wplain, a.n2v_fmax)));
+#pragma unroll 1
+  for (;;) {
+    const uint32_t kmin = __reduce_min_sync(0xFFFFFFFFu, klo);
+    if (kmin == 0xFFFFFFFFu || kmin > best.key) break;  // equal keys still need a look: the lower id wins
+    const uint32_t L = (uint32_t)__ffs((int)__ballot_sync(0xFFFFFFFFu, klo == kmin)) - 1u;
+    float b0, b1;
+    const float W = n2v_strip_exact<CLEAN>(a, c, s, L, lane, b0, b1);
+    const uint32_t xL = __shfl_sync(0xFFFFFFFFu, x, (int)L), pL = __shfl_sync(0xFFFFFFFFu, pw, (int)L);
+    if (W > 0.0f) {
+      const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(xL), W));
+      const uint32_t id = s * 32u + L;
+      if (bits < best.key || (bits == best.key && id < best.id)) { best.key = bits; best.id = id; best.pick = pL; best.W = W; }
+    }
+    if (lane == L) klo = 0xFFFFFFFFu;  // evaluated
+  }
+}
+
+// node2vec: inverse-CDF pick inside the winning strip B from its exact biases, spread over the
+// warp in canonical order (lane 0 (b0, b1), lane 1 (b0, b1), ...): the first edge whose running
+// sum exceeds u * W.
+template <bool CLEAN>
+__device__ __forceinline__ uint32_t n2v_pick(const WalkArgs& a, const StepCtx& c, uint32_t B, uint32_t pick,
+                                             uint32_t lane) {
+  const uint32_t sB = B >> 5, lB = B & 31u;
+  float b0, b1;
+  const float W = n2v_strip_exact<CLEAN>(a, c, sB, lB, lane, b0, b1);
+  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
+  float acc = 0.0f;
+  uint32_t cnt = 0;
+#pragma unroll 1
+  for (int t = 0; t < 32; ++t) {
+    acc = __fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, b0, t)); cnt += acc <= thr ? 1u : 0u;
+    acc = __fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, b1, t)); cnt += acc <= thr ? 1u : 0u;
+    if (cnt < 2u * (uint32_t)(t + 1)) break;  // found (warp-uniform)
+  }
+  if (cnt >= 64u) {  // rounding pushed u * W past the sequential total: the strip's last positive edge
+    const uint32_t m1 = __ballot_sync(0xFFFFFFFFu, b1 > 0.0f), m0 = __ballot_sync(0xFFFFFFFFu, b0 > 0.0f);
+    const int t1 = 31 - __clz((int)m1), t0 = 31 - __clz((int)m0);  // -1 when the mask is empty
+    cnt = t1 >= t0 ? 2u * (uint32_t)t1 + 1u : 2u * (uint32_t)t0;
+  }
+  // position z = 4 j + k of the strip: quad 512 s + 32 j + l, edge k
+  return 4u * (sB * fw::kQuadsPerSuper + 32u * (cnt >> 2) + lB) + (cnt & 3u);
+}
+
+// The sweep of node2vec reads plain weights (DeepWalk's bias); its own bias enters per strip.
+template <int APP>
+struct SweepApp { static constexpr int value = APP == FW_APP_NODE2VEC ? FW_APP_DEEPWALK : APP; };
+
 // A lane's running state while a row is swept: the partial sums of the current supergroup
 // and the Philox block that serves it.
 struct SuperAcc {
@@ -436,8 +543,10 @@ struct SuperAcc {
 
 // Adds sub-block b's partial sum A; at the end of a supergroup (or of the row) forms the strip's
 // total (A0+A1)+(A2+A3) and tests its key, behind the lower-bound filter when `filtered`.
-__device__ __forceinline__ void absorb(const WalkArgs& a, SuperAcc& s, Best& best, float A, uint32_t b, bool row_end,
-                                       bool filtered, uint32_t lane, uint32_t c1, uint32_t qlo, uint32_t qhi) {
+template <int APP, bool CLEAN>
+__device__ __forceinline__ void absorb(const WalkArgs& a, const StepCtx& c, SuperAcc& s, Best& best, float A,
+                                       uint32_t b, bool row_end, bool filtered, uint32_t lane, uint32_t c1,
+                                       uint32_t qlo, uint32_t qhi) {
   const uint32_t u = b & 3u;
   if (u == 0u) s.p01 = A;
   else if (u == 1u) s.p01 = __fadd_rn(s.p01, A);
@@ -446,7 +555,8 @@ __device__ __forceinline__ void absorb(const WalkArgs& a, SuperAcc& s, Best& bes
     const float W = u == 3u ? __fadd_rn(s.p01, __fadd_rn(s.a2, A)) : u == 2u ? __fadd_rn(s.p01, s.a2) : s.p01;
     const uint32_t x = s.m == 0u ? s.r.x : s.m == 1u ? s.r.y : s.r.z;
     const uint32_t id = (b >> 2) * 32u + lane;
-    if (filtered) offer_filtered(best, x, s.r.w, W, id, __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key)));
+    if (APP == FW_APP_NODE2VEC && c.prev >= 0) n2v_test<CLEAN>(a, c, b >> 2, lane, W, x, s.r.w, best);
+    else if (filtered) offer_filtered(best, x, s.r.w, W, id, __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key)));
     else offer(best, x, s.r.w, W, id);
     if (!row_end) {
       if (++s.m == 3u) { s.m = 0u; s.r = fw::philox4x32_10((++s.g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
@@ -570,7 +680,7 @@ __device__ __forceinline__ bool sweep_supers(const WalkArgs& a, const StepCtx& c
   if (uses_ring<APP>() && lane == 0) {
 #pragma unroll
     for (uint32_t t = 0; t < kStages; ++t)
-      if (b0 + t < bend) ring_fill<APP>(c, ring, b0 + t, t);
+      if (b0 + t < bend) ring_fill<SweepApp<APP>::value>(c, ring, b0 + t, t);
   }
   SuperAcc acc{0.0f, 0.0f, s0 / 3u, s0 % 3u, fw::Philox4{0u, 0u, 0u, 0u}};
   acc.r = fw::philox4x32_10(acc.g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
@@ -579,12 +689,12 @@ __device__ __forceinline__ bool sweep_supers(const WalkArgs& a, const StepCtx& c
   for (uint32_t b = b0; b < bend; ++b) {
     float A;
     if (uses_ring<APP>()) {
-      if (!ring_sub<APP, CLEAN>(a, c, b, bend, lane, ring, ring_ptr, t, A)) return false;
+      if (!ring_sub<SweepApp<APP>::value, CLEAN>(a, c, b, bend, lane, ring, ring_ptr, t, A)) return false;
       t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
     } else {
-      A = sub_global<APP, CLEAN>(a, c, b, lane);
+      A = sub_global<SweepApp<APP>::value, CLEAN>(a, c, b, lane);
     }
-    absorb(a, acc, best, A, b, false, true, lane, c1, qlo, qhi);
+    absorb<APP, CLEAN>(a, c, acc, best, A, b, false, true, lane, c1, qlo, qhi);
   }
   return true;
 }
@@ -618,14 +728,6 @@ __device__ __noinline__ uint32_t coop_serve(const WalkArgs& args, CoopTask* task
       const uint32_t s0 = s1 > kCoopChunkSupers + 1u ? s1 - kCoopChunkSupers : 1u;
       StepCtx c = task->c;
       c.flags = my_flags;
-      if (APP == FW_APP_NODE2VEC && c.prev >= 0) {
-        // the membership windows chain through the row in ascending order: start this chunk's
-        // chain at the first entry of prev's row that is not below the chunk's first neighbour id
-        int32_t first = 0;
-        if (lane == 0) first = __ldg(reinterpret_cast<const int32_t*>(c.sec + (size_t)s0 * fw::kQuadsPerSuper));
-        first = __shfl_sync(0xFFFFFFFFu, first, 0);
-        c.from = warp_lower_bound(c.prow, 0u, c.plen, first, lane);
-      }
       fine = sweep_supers<APP, CLEAN>(a, c, s0, s1, lane, task->c1, task->qlo, task->qhi, ring, ring_ptr, best);
       warp_argmin(best.key, best.id);
     }
@@ -719,143 +821,17 @@ __device__ __noinline__ unsigned long long strip_redo(const WalkArgs& args, Step
   const uint32_t sW = B >> 5, lW = B & 31u;
   const uint32_t last_b = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub - 1u;
   const uint32_t pick = fw::philox4x32_10((sW / 3u) * 32u + lW, c1, qlo, qhi, a.k0, a.k1).w;
-  if (APP == FW_APP_NODE2VEC) c.from = 0u;
   float A[4];
 #pragma unroll 1
   for (uint32_t i = 0; i < 4u; ++i) {
     const uint32_t b = 4u * sW + i;
     A[i] = 0.0f;
     if (b <= last_b) {  // warp-uniform
-      A[i] = sub_global<APP, CLEAN>(a, c, b, APP == FW_APP_NODE2VEC ? lane : lW);
-      if (APP == FW_APP_NODE2VEC) A[i] = __shfl_sync(0xFFFFFFFFu, A[i], (int)lW);
+      A[i] = sub_global<SweepApp<APP>::value, CLEAN>(a, c, b, lW);
     }
   }
   const float W = __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3]));
   return ((unsigned long long)pick << 32) | __float_as_uint(W);
-}
-
-// ---- node2vec: sweep with the membership test only where it can matter ----
-//
-// bias = w * f with f in {1/p, 1, 1/q}, so a strip's total bias W is at most fmax * sum(w) and
-// its key E / W at least E / (fmax * sum(w)).  The sweep therefore adds up the plain weights
-// only (no neighbour ids, no membership test) and looks closer only at strips whose optimistic
-// key could still beat the best true key so far: a handful per row.  A strip that is skipped has
-// a true key above the final minimum, so the result is the one the full evaluation gives.  The reference evaluates the membership test for every
-// candidate of every row (include/app.cuh:109-122).
-
-// Exact biases of strip (s, L) spread over the warp: lane t holds edges 2*(t&1), 2*(t&1)+1 of the
-// strip's quad t>>1, i.e. the strip's 64 edges in canonical order are lane 0 (b0, b1), lane 1
-// (b0, b1), ...  Membership by one binary search over prev's row per edge (two per lane, run side
-// by side).  Returns the strip's total in the canonical summation order, identical on all lanes.
-template <bool CLEAN>
-__device__ __forceinline__ float n2v_strip_exact(const WalkArgs& a, const StepCtx& c, uint32_t s, uint32_t L,
-                                                 uint32_t lane, float& b0, float& b1) {
-  const uint32_t q = s * fw::kQuadsPerSuper + 32u * (lane >> 1) + L;
-  const uint32_t k0 = 2u * (lane & 1u);
-  b0 = 0.0f;
-  b1 = 0.0f;
-  int32_t x0 = 0, x1 = 0;
-  const uint32_t r0 = 4u * q + k0;
-  const bool v0 = q < c.nq && r0 >= c.head && r0 < c.tail;
-  const bool v1 = q < c.nq && r0 + 1u >= c.head && r0 + 1u < c.tail;
-  if (q < c.nq) {
-    // the lane's two edges are the low or the high half of the quad: one 8-byte load each
-    const float2 w = __ldg(reinterpret_cast<const float2*>(c.prim + q) + (lane & 1u));
-    const int2 x = __ldg(reinterpret_cast<const int2*>(c.sec + q) + (lane & 1u));
-    b0 = w.x; b1 = w.y; x0 = x.x; x1 = x.y;
-  }
-  // lower bounds of x0 and x1 in prev's row, both searches advancing together
-  uint32_t lo0 = 0, hi0 = v0 && x0 != c.prev ? c.plen : 0u;
-  uint32_t lo1 = 0, hi1 = v1 && x1 != c.prev ? c.plen : 0u;
-  while (lo0 < hi0 || lo1 < hi1) {
-    const uint32_t m0 = lo0 + ((hi0 - lo0) >> 1), m1 = lo1 + ((hi1 - lo1) >> 1);
-    const int32_t p0 = lo0 < hi0 ? __ldg(c.prow + m0) : 0;
-    const int32_t p1 = lo1 < hi1 ? __ldg(c.prow + m1) : 0;
-    if (lo0 < hi0) { if (p0 < x0) lo0 = m0 + 1u; else hi0 = m0; }
-    if (lo1 < hi1) { if (p1 < x1) lo1 = m1 + 1u; else hi1 = m1; }
-  }
-  const bool linked0 = v0 && x0 != c.prev && lo0 < c.plen && __ldg(c.prow + lo0) == x0;
-  const bool linked1 = v1 && x1 != c.prev && lo1 < c.plen && __ldg(c.prow + lo1) == x1;
-  b0 = !v0 ? 0.0f : x0 == c.prev ? __fmul_rn(b0, a.inv_p) : linked0 ? b0 : __fmul_rn(b0, a.inv_q);
-  b1 = !v1 ? 0.0f : x1 == c.prev ? __fmul_rn(b1, a.inv_p) : linked1 ? b1 : __fmul_rn(b1, a.inv_q);
-  if (!CLEAN) { b0 = pos(b0); b1 = pos(b1); }
-  // (w0+w1)+(w2+w3) per quad, (S0+S1)+(S2+S3) per sub-block, (A0+A1)+(A2+A3): a butterfly
-  float t = __fadd_rn(b0, b1);
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const float o = __shfl_xor_sync(0xFFFFFFFFu, t, d);
-    t = (lane & d) ? __fadd_rn(o, t) : __fadd_rn(t, o);  // same operands in the same order on both lanes
-  }
-  return t;
-}
-
-// One weighted pick for node2vec from the second step on (c.prev >= 0), rows of more than 32 quads.
-// `r` is the lane's Philox block 0.  Returns the edge index relative to quad 0 or 0xFFFFFFFF.
-//
-// Per supergroup every lane forms the optimistic key of its strip, E / (fmax * sum of plain
-// weights), which is never above the strip's true key.  Strips are then evaluated exactly in the
-// order of their optimistic keys, and only while that key does not exceed the best true key found
-// so far: usually one or two strips in the first supergroup of a row and none in the others.
-template <bool CLEAN>
-__device__ __forceinline__ uint32_t sample_row_n2v(const WalkArgs& a, const StepCtx& c, fw::Philox4 r, uint32_t c1,
-                                                   uint32_t qlo, uint32_t qhi, uint32_t lane) {
-  const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
-  const uint32_t last_b = nb - 1u;
-  const uint32_t nsuper = (nb + 3u) >> 2;
-  uint32_t best_key = 0xFFFFFFFFu, best_id = 0xFFFFFFFFu, best_pick = 0u;  // warp-uniform
-  uint32_t g = 0, m = 0;
-#pragma unroll 1
-  for (uint32_t s = 0; s < nsuper; ++s) {
-    float A[4];
-#pragma unroll
-    for (uint32_t i = 0; i < 4u; ++i) {
-      const uint32_t b = 4u * s + i;
-      A[i] = b <= last_b ? sub_global<FW_APP_DEEPWALK, CLEAN>(a, c, b, lane) : 0.0f;  // warp-uniform test
-    }
-    const float Wplain = __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3]));
-    const uint32_t x = m == 0u ? r.x : m == 1u ? r.y : r.z;
-    // optimistic key bits; 0xFFFFFFFF = nothing to evaluate in this lane
-    uint32_t klo = 0xFFFFFFFFu;
-    if (Wplain > 0.0f) klo = __float_as_uint(__fdiv_rn(fw::exp_key(x), __fmul_rn(Wplain, a.n2v_fmax)));
-#pragma unroll 1
-    for (;;) {
-      const uint32_t kmin = __reduce_min_sync(0xFFFFFFFFu, klo);
-      if (kmin == 0xFFFFFFFFu || kmin > best_key) break;  // equal keys still need a look: the lower id wins
-      const uint32_t L = (uint32_t)__ffs((int)__ballot_sync(0xFFFFFFFFu, klo == kmin)) - 1u;
-      float b0, b1;
-      const float W = n2v_strip_exact<CLEAN>(a, c, s, L, lane, b0, b1);
-      const uint32_t xL = __shfl_sync(0xFFFFFFFFu, x, (int)L), pL = __shfl_sync(0xFFFFFFFFu, r.w, (int)L);
-      if (W > 0.0f) {
-        const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(xL), W));
-        const uint32_t id = s * 32u + L;
-        if (bits < best_key || (bits == best_key && id < best_id)) { best_key = bits; best_id = id; best_pick = pL; }
-      }
-      if (lane == L) klo = 0xFFFFFFFFu;  // evaluated
-    }
-    if (++m == 3u) { m = 0u; r = fw::philox4x32_10((++g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
-  }
-  const uint32_t B = best_id;
-  if (B == 0xFFFFFFFFu) return B;
-  // pick inside the winning strip: its exact biases again, spread over the warp in canonical order
-  const uint32_t sB = B >> 5, lB = B & 31u;
-  float b0, b1;
-  const float W = n2v_strip_exact<CLEAN>(a, c, sB, lB, lane, b0, b1);
-  const float thr = __fmul_rn((float)(best_pick >> 8) * 0x1p-24f, W);
-  float acc = 0.0f;
-  uint32_t cnt = 0;
-#pragma unroll 1
-  for (int t = 0; t < 32; ++t) {
-    acc = __fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, b0, t)); cnt += acc <= thr ? 1u : 0u;
-    acc = __fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, b1, t)); cnt += acc <= thr ? 1u : 0u;
-    if (cnt < 2u * (uint32_t)(t + 1)) break;  // found (warp-uniform)
-  }
-  if (cnt >= 64u) {  // rounding pushed u * W past the sequential total: the strip's last positive edge
-    const uint32_t m1 = __ballot_sync(0xFFFFFFFFu, b1 > 0.0f), m0 = __ballot_sync(0xFFFFFFFFu, b0 > 0.0f);
-    const int t1 = 31 - __clz((int)m1), t0 = 31 - __clz((int)m0);  // -1 when the mask is empty
-    cnt = t1 >= t0 ? 2u * (uint32_t)t1 + 1u : 2u * (uint32_t)t0;
-  }
-  // position z = 4 j + k of the strip: quad 512 s + 32 j + l, edge k
-  return 4u * (sB * fw::kQuadsPerSuper + 32u * (cnt >> 2) + lB) + (cnt & 3u);
 }
 
 // One weighted pick in the row described by c, by one warp.  Returns the
@@ -923,14 +899,13 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   // global memory (boundary quads, partial fill), the interior ones through the ring when
   // there are any.  Four sub-blocks make a supergroup; a lane's four partial sums A0..A3 are
   // combined as (A0+A1)+(A2+A3) and tested once per supergroup.
-  if (APP == FW_APP_NODE2VEC && c.prev >= 0) return sample_row_n2v<CLEAN>(a, c, r, c1, qlo, qhi, lane);
   const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
   const uint32_t last_b = nb - 1u;
   const bool ringed = uses_ring<APP>() && nb >= 3u;
   if (ringed && lane == 0) {
 #pragma unroll
     for (uint32_t t = 0; t < kStages; ++t)
-      if (1u + t < last_b) ring_fill<APP>(c, ring, 1u + t, t);
+      if (1u + t < last_b) ring_fill<SweepApp<APP>::value>(c, ring, 1u + t, t);
   }
   SuperAcc acc{0.0f, 0.0f, 0u, 0u, r};
   // A very long row is posted for the CTA's idle warps, which take supergroups from the back.
@@ -945,13 +920,13 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     if (lane == 0) k = ld_volatile(&task->ticket) & 0xFFFFu;
     return (b >> 2) + __shfl_sync(0xFFFFFFFFu, k, 0) * kCoopChunkSupers >= end_super;
   };
-  absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
+  absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
   uint32_t b = 1;
   if (!ringed) {
 #pragma unroll 1
     for (; b < last_b; ++b) {
       if (posted && (b & 3u) == 0u && taken(b)) break;
-      absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, b, lane), b, false, true, lane, c1, qlo, qhi);
+      absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, b, lane), b, false, true, lane, c1, qlo, qhi);
     }
   } else {
     uint32_t t = 0;
@@ -971,11 +946,11 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
         break;
       }
       float A;
-      if (!ring_sub<APP, CLEAN>(a, c, b, last_b, lane, ring, ring_ptr, t, A)) {
+      if (!ring_sub<SweepApp<APP>::value, CLEAN>(a, c, b, last_b, lane, ring, ring_ptr, t, A)) {
         ring.failed = true;
         return 0xFFFFFFFFu;
       }
-      absorb(a, acc, best, A, b, false, true, lane, c1, qlo, qhi);
+      absorb<APP, CLEAN>(a, c, acc, best, A, b, false, true, lane, c1, qlo, qhi);
       t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
     }
   }
@@ -987,19 +962,12 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
       acc.g = end_super / 3u;
       acc.m = end_super - 3u * acc.g;
       acc.r = fw::philox4x32_10(acc.g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
-      if (APP == FW_APP_NODE2VEC && c.prev >= 0) {
-        // the chain of membership windows was cut by the helpers' part: restart it here
-        int32_t first = 0;
-        if (lane == 0) first = __ldg(reinterpret_cast<const int32_t*>(c.sec + (size_t)end_super * fw::kQuadsPerSuper));
-        first = __shfl_sync(0xFFFFFFFFu, first, 0);
-        c.from = warp_lower_bound(c.prow, 0u, c.plen, first, lane);
-      }
 #pragma unroll 1
       for (b = 4u * end_super; b < last_b; ++b)
-        absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, b, lane), b, false, false, lane, c1, qlo, qhi);
+        absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, b, lane), b, false, false, lane, c1, qlo, qhi);
     }
   }
-  if (nb > 1u) absorb(a, acc, best, sub_global<APP, CLEAN>(a, c, last_b, lane), last_b, true, false, lane, c1, qlo, qhi);
+  if (nb > 1u) absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, last_b, lane), last_b, true, false, lane, c1, qlo, qhi);
   warp_argmin(best.key, best.id);
   uint32_t B = best.id;
   if (posted) {
@@ -1009,12 +977,15 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     B = (uint32_t)fin;
     if (B != 0xFFFFFFFFu && fin != own) {  // another warp reduced the winning strip
       const unsigned long long pw = strip_redo<APP, CLEAN>(a, c, B, c1, qlo, qhi, lane);
-      return pick_in_row<APP, CLEAN>(a, c, B, (uint32_t)(pw >> 32), __uint_as_float((uint32_t)pw), lane);
+      if (APP == FW_APP_NODE2VEC && c.prev >= 0) return n2v_pick<CLEAN>(a, c, B, (uint32_t)(pw >> 32), lane);
+      return pick_in_row<SweepApp<APP>::value, CLEAN>(a, c, B, (uint32_t)(pw >> 32), __uint_as_float((uint32_t)pw), lane);
     }
   }
   if (B == 0xFFFFFFFFu) return B;
-  return pick_in_row<APP, CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)),
-                                 __shfl_sync(0xFFFFFFFFu, best.W, (int)(B & 31u)), lane);
+  if (APP == FW_APP_NODE2VEC && c.prev >= 0)
+    return n2v_pick<CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)), lane);
+  return pick_in_row<SweepApp<APP>::value, CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)),
+                                                  __shfl_sync(0xFFFFFFFFu, best.W, (int)(B & 31u)), lane);
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
@@ -1023,7 +994,7 @@ __global__ void __launch_bounds__(kThreads, MODE != FW_GROUP_EDGE && APP != FW_A
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE && uses_ring<APP>() ? kStages * stage_bytes<APP>() : 0u;
+  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE ? kStages * stage_bytes<SweepApp<APP>::value>() : 0u;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
   Ring ring;
@@ -1165,8 +1136,7 @@ inline KernelFn pick_kernel(int app, int mode, bool clean, bool shared, int xadj
 // Dynamic shared memory of one CTA: the warps' rings, then the histogram.
 inline size_t kernel_smem_bytes(int app, int mode, int d, bool hist_in_smem) {
   size_t ring = 0;
-  if (mode != FW_GROUP_EDGE && (app != FW_APP_NODE2VEC || FW_N2V_RING != 0))
-    ring = (size_t)kWarpsPerCta * kStages * (app == FW_APP_NODE2VEC ? 2u * kSubBytes : kSubBytes);
+  if (mode != FW_GROUP_EDGE) ring = (size_t)kWarpsPerCta * kStages * kSubBytes;
   return ring + (hist_in_smem ? (size_t)(d + 1) * 4 : 0);
 }
 
