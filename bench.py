@@ -14,7 +14,6 @@ resident in HBM; `e2e` is the same through fw_walk_batch_into with pinned host b
 (start vertices copied in, the whole walk table copied out, four double-buffered batches).
 """
 import argparse
-import ctypes
 import json
 import os
 import statistics

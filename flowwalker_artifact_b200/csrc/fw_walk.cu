@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <mutex>
 #include <new>
 
 #include "fw_internal.h"
@@ -35,6 +36,7 @@ static constexpr int64_t kSharingAutoDegree = 262144;
 // ---------------------------------------------------------------------------
 
 struct fw_engine {
+  std::mutex mu;  // an engine serves one walk call at a time; calls from several threads queue here
   int device = 0;
   int sms = 0;
   int64_t V = 0, E = 0;
@@ -50,7 +52,7 @@ struct fw_engine {
   unsigned long long* h_scratch = nullptr;  // pinned mirror
   size_t scratch_words = 0;
   cudaStream_t stream = nullptr, stream2 = nullptr;
-  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   // staging for the host-buffer entry points (grown on demand)
   int32_t* d_starts[2] = {nullptr, nullptr};
   int32_t* d_result[2] = {nullptr, nullptr};
@@ -273,6 +275,7 @@ extern "C" int fw_walk_device(fw_engine* e, const fw_walk_params* p, const int32
   int rc = check_params(e, p, n);
   if (rc) return rc;
   if (n > 0 && (!starts_dev || !result_dev)) return fw::fail(FW_ERR_ARG, "null device buffer");
+  std::lock_guard<std::mutex> lock(e->mu);
   DeviceGuard guard(e->device);
   rc = ensure_scratch(e, p->d);
   if (rc) return rc;
@@ -293,6 +296,7 @@ extern "C" int fw_walk(fw_engine* e, const fw_walk_params* p, const int32_t* sta
   int rc = check_params(e, p, n);
   if (rc) return rc;
   if (n > 0 && (!starts_host || !result_host)) return fw::fail(FW_ERR_ARG, "null host buffer");
+  std::lock_guard<std::mutex> lock(e->mu);
   DeviceGuard guard(e->device);
   rc = ensure_scratch(e, p->d);
   if (rc) return rc;
@@ -326,6 +330,7 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
                         int64_t batch_size, int32_t headroom_mb, int32_t* pinned, fw_walk_stats* stats,
                         uint64_t* len_hist) {
   int rc = FW_OK;
+  std::lock_guard<std::mutex> lock(e->mu);
   DeviceGuard guard(e->device);
   const size_t D = (size_t)p->d + 1;
   if (batch_size <= 0) {  // --autobatch, src/main.cu:259-271
@@ -354,9 +359,7 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
   unsigned long long* hsc[2] = {e->h_scratch, e->h_scratch + words};
   if (stats) { stats->steps = 0; stats->scanned = 0; stats->device_ms = 0; stats->total_ms = 0; stats->device_status = 0; stats->launches = 0; }
   if (len_hist) for (size_t z = 0; z < D; ++z) len_hist[z] = 0;
-  cudaEvent_t t0 = nullptr, t1 = nullptr;
-  if (cudaEventCreate(&t0) != cudaSuccess || cudaEventCreate(&t1) != cudaSuccess)
-    return bail(fw::fail(FW_ERR_CUDA, "cudaEventCreate failed"));
+  cudaEvent_t t0 = e->ev[4], t1 = e->ev[5];
   cudaEventRecord(t0, streams[0]);
   bool pending[2] = {false, false};
   auto drain = [&](int s) -> int {
@@ -393,7 +396,6 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
     cudaEventElapsedTime(&total, t0, t1);
     if (stats) stats->total_ms = total;
   }
-  cudaEventDestroy(t0); cudaEventDestroy(t1);
   if (rc) return bail(rc);
   return FW_OK;
 }
@@ -495,6 +497,8 @@ int noalloc_scratch_for(int device, unsigned long long** out) {
   if (device < 0 || device >= kNoAllocMaxDevices)
     return fw::fail(FW_ERR_ARG, "device ordinal %d is beyond the %d this entry point supports", device,
                     kNoAllocMaxDevices);
+  static std::mutex table_mu;
+  std::lock_guard<std::mutex> lock(table_mu);
   if (!g_noalloc_ptr[device]) {
     void* p = nullptr;
     cudaError_t err = cudaGetSymbolAddress(&p, g_noalloc_scratch);

@@ -3,7 +3,8 @@
  *
  * Plain C types only: pointers, sizes and PODs.  Every function returns an
  * int status (FW_OK = 0, negative = error; the message is available from
- * fw_last_error() on the calling thread) and never calls exit().  Objects
+ * fw_last_error() on the calling thread) and never calls exit().  Calls on one engine from
+ * several threads are serialised inside the library; different engines run concurrently.  Objects
  * created by a *_create / *_load / *_generate call are released by the matching
  * *_destroy.  Buffers passed in stay owned by the caller.
  *
