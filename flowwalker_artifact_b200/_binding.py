@@ -60,6 +60,8 @@ def lib():
         L.fw_graph_load.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(vp)]
         L.fw_graph_save.argtypes = [vp, ctypes.c_char_p]
         L.fw_graph_from_arrays.argtypes = [i64, i64, vp, ctypes.c_int, vp, vp, vp, ctypes.POINTER(vp)]
+        L.fw_graph_from_edgelist.argtypes = [ctypes.c_char_p, i32, ctypes.c_float, ctypes.c_float,
+                                             ctypes.c_uint64, ctypes.POINTER(vp)]
         L.fw_rmat_generate.argtypes = [ctypes.POINTER(_Rmat), ctypes.POINTER(vp)]
         L.fw_graph_info.argtypes = [vp, ctypes.POINTER(i64), ctypes.POINTER(i64), ctypes.POINTER(i32),
                                     ctypes.POINTER(i32), ctypes.POINTER(i32)]
@@ -132,6 +134,12 @@ class Graph:
     def load(cls, prefix, need_weight=True, need_label=False):
         h = ctypes.c_void_p()
         _check(lib().fw_graph_load(os.fsencode(prefix), int(need_weight), int(need_label), h))
+        return cls(h.value)
+
+    @classmethod
+    def from_edgelist(cls, path, n_labels=5, weight_range=(1.0, 5.0), seed=1):
+        h = ctypes.c_void_p()
+        _check(lib().fw_graph_from_edgelist(os.fsencode(path), n_labels, weight_range[0], weight_range[1], seed, h))
         return cls(h.value)
 
     @classmethod

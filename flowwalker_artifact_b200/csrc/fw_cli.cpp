@@ -56,6 +56,8 @@ void define_flags(fwflags::Parser& fl) {
   fl.add("group", Flag::kInt, "0", "sampler granularity: 0 default, 1 per neighbour, 64 per strip");
   fl.add("gpus", Flag::kInt, "1", "number of GPUs: queries are sharded, the graph is replicated");
   fl.add("save_result", Flag::kString, "", "write the int32 [n x (d+1)] walk table to this file");
+  fl.add("edgelist", Flag::kString, "", "build the graph from this text edge list instead of reading --input");
+  fl.add("save_csr", Flag::kString, "", "write the graph as <prefix>_xadj/_edge/_weight/_label.bin and exit");
 }
 
 bool parse_schema(const std::string& text, std::vector<int32_t>* out) {
@@ -163,13 +165,23 @@ int main(int argc, char** argv) {
 
   const bool metapath = fl.b("metapath");
   const int apps = (int)fl.b("deepwalk") + (int)fl.b("ppr") + (int)fl.b("node2vec") + (int)metapath;
-  if (apps != 1) { printf("Please choose a walk mode\n"); return 0; }  // src/walk.cu:563-566
+  if (apps != 1 && fl.s("save_csr").empty()) { printf("Please choose a walk mode\n"); return 0; }  // src/walk.cu:563-566
   const int app = fl.b("deepwalk") ? FW_APP_DEEPWALK : fl.b("ppr") ? FW_APP_PPR
                 : fl.b("node2vec") ? FW_APP_NODE2VEC : FW_APP_METAPATH;
 
   // graph: weights xor labels, as include/graph.cuh:145-185
   fw_graph* g = nullptr;
-  if (fw_graph_load(fl.s("input").c_str(), !metapath && !fl.b("lognorm"), metapath, &g) != FW_OK) return fail("load");
+  if (!fl.s("edgelist").empty()) {  // the job of data/EdgeListToCSR.cpp
+    if (fw_graph_from_edgelist(fl.s("edgelist").c_str(), 5, 1.0f, 5.0f, 1, &g) != FW_OK) return fail("edge list");
+  } else if (fw_graph_load(fl.s("input").c_str(), !metapath && !fl.b("lognorm"), metapath, &g) != FW_OK) {
+    return fail("load");
+  }
+  if (!fl.s("save_csr").empty()) {
+    if (fw_graph_save(g, fl.s("save_csr").c_str()) != FW_OK) return fail("save");
+    printf("wrote %s_{xadj,edge,weight,label}.bin\n", fl.s("save_csr").c_str());
+    fw_graph_destroy(g);
+    return 0;
+  }
   GraphView gv;
   fw_graph_info(g, &gv.V, &gv.E, &gv.bits, nullptr, nullptr);
   fw_graph_arrays(g, &gv.xadj, &gv.adj, &gv.weight, &gv.label);

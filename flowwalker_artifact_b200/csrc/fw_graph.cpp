@@ -15,9 +15,13 @@
 #include <string.h>
 #include <sys/stat.h>
 
+#include <algorithm>
 #include <string>
+#include <unordered_map>
+#include <vector>
 
 #include "fw_internal.h"
+#include "fw_spec.cuh"
 
 namespace fw {
 static thread_local char g_err[512] = "";
@@ -235,5 +239,93 @@ extern "C" int fw_graph_max_degree(const fw_graph* g, int64_t* vertex, int64_t* 
   }
   if (vertex) *vertex = arg;
   if (degree) *degree = best < 0 ? 0 : best;
+  return FW_OK;
+}
+
+// Edge list -> CSR with the conventions of the reference's converter (data/EdgeListToCSR.cpp:132-268):
+// the graph is made undirected, duplicate edges are dropped, vertices are renumbered in order of
+// first appearance (so vertices without an edge disappear), and every undirected edge gets one
+// label and one weight shared by its two directions.  Differences, on purpose: rows come out
+// sorted by neighbour id (node2vec's membership test needs that; the reference appends in input
+// order), self-loops are dropped, and labels / weights are seeded (Philox keyed by the
+// undirected edge's rank) instead of drawn from std::random_device.
+extern "C" int fw_graph_from_edgelist(const char* path, int32_t n_labels, float weight_lo, float weight_hi,
+                                      uint64_t seed, fw_graph** out) {
+  fw::clear_error();
+  if (!path || !out) return fw::fail(FW_ERR_ARG, "fw_graph_from_edgelist: null argument");
+  *out = nullptr;
+  FILE* f = fopen(path, "r");
+  if (!f) return fw::fail(FW_ERR_IO, "cannot open %s: %s", path, strerror(errno));
+  std::unordered_map<long long, int32_t> renum;
+  std::vector<uint64_t> und;  // (min << 32 | max) of the renumbered endpoints
+  char line[512];
+  long long lineno = 0;
+  while (fgets(line, sizeof(line), f)) {
+    ++lineno;
+    const char* p = line;
+    while (*p == ' ' || *p == '\t') ++p;
+    if (*p == '#' || *p == '%' || *p == '\n' || *p == '\r' || *p == 0) continue;
+    long long u, v;
+    if (sscanf(p, "%lld %lld", &u, &v) != 2) {
+      fclose(f);
+      return fw::fail(FW_ERR_IO, "%s:%lld: expected two vertex ids", path, lineno);
+    }
+    if (u == v) continue;
+    int32_t ids[2];
+    const long long raw[2] = {u, v};
+    for (int k = 0; k < 2; ++k) {
+      auto it = renum.find(raw[k]);
+      if (it == renum.end()) {
+        if (renum.size() >= (size_t)INT32_MAX) { fclose(f); return fw::fail(FW_ERR_ARG, "more than 2^31-1 vertices"); }
+        it = renum.emplace(raw[k], (int32_t)renum.size()).first;
+      }
+      ids[k] = it->second;
+    }
+    const uint32_t lo = (uint32_t)std::min(ids[0], ids[1]), hi = (uint32_t)std::max(ids[0], ids[1]);
+    und.push_back((uint64_t)lo << 32 | hi);
+  }
+  fclose(f);
+  std::sort(und.begin(), und.end());
+  und.erase(std::unique(und.begin(), und.end()), und.end());
+  const int64_t V = (int64_t)renum.size(), E = 2 * (int64_t)und.size();
+  if (E > 0xFFFFFFFFll) return fw::fail(FW_ERR_ARG, "more than 2^32-1 directed edges");
+  struct Half { uint64_t key; uint32_t rank; };  // key = src << 32 | dst, rank = undirected edge
+  std::vector<Half> half;
+  half.reserve((size_t)E);
+  for (size_t r = 0; r < und.size(); ++r) {
+    const uint32_t lo = (uint32_t)(und[r] >> 32), hi = (uint32_t)und[r];
+    half.push_back({(uint64_t)lo << 32 | hi, (uint32_t)r});
+    half.push_back({(uint64_t)hi << 32 | lo, (uint32_t)r});
+  }
+  std::sort(half.begin(), half.end(), [](const Half& a, const Half& b) { return a.key < b.key; });
+  fw_graph* g = new fw_graph();
+  g->V = V; g->E = E; g->xadj_bits = 32;
+  const bool weights = weight_hi > weight_lo, labels = n_labels > 0;
+  g->xadj = malloc(4 * (size_t)(V + 1));
+  g->adj = (int32_t*)malloc(E ? 4 * (size_t)E : 1);
+  if (weights) g->weight = (float*)malloc(E ? 4 * (size_t)E : 1);
+  if (labels) g->label = (int32_t*)malloc(E ? 4 * (size_t)E : 1);
+  if (!g->xadj || !g->adj || (weights && !g->weight) || (labels && !g->label)) {
+    fw_graph_destroy(g);
+    return fw::fail(FW_ERR_NOMEM, "out of host memory");
+  }
+  uint32_t* xadj = (uint32_t*)g->xadj;
+  int64_t e = 0;
+  for (int64_t v = 0; v <= V; ++v) {
+    while (e < E && (int64_t)(half[(size_t)e].key >> 32) < v) ++e;
+    xadj[v] = (uint32_t)e;
+  }
+  const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  for (e = 0; e < E; ++e) {
+    const Half& h = half[(size_t)e];
+    g->adj[e] = (int32_t)(uint32_t)h.key;
+    const fw::Philox4 r = fw::philox4x32_10(h.rank, 0u, 0u, 0x45u, k0, k1);
+    if (weights) {
+      const float w = fmaf((float)(r.x >> 8) * 0x1p-24f, weight_hi - weight_lo, weight_lo);
+      g->weight[e] = w >= weight_hi ? weight_lo : w;
+    }
+    if (labels) g->label[e] = (int32_t)(((uint64_t)r.y * (uint32_t)n_labels) >> 32);
+  }
+  *out = g;
   return FW_OK;
 }

@@ -110,6 +110,11 @@ int fw_graph_from_arrays(int64_t V, int64_t E, const void* xadj, int xadj_bits,
                          const int32_t* adj, const float* weight,
                          const int32_t* label, fw_graph** out);
 int fw_rmat_generate(const fw_rmat_params* params, fw_graph** out);
+/* Text edge list ("u v" per line, '#' or '%' comments) -> undirected, deduplicated CSR with vertices
+ * renumbered by first appearance and one label / weight per undirected edge, as the reference's
+ * converter does (data/EdgeListToCSR.cpp:132-268); rows sorted, self-loops dropped, attributes seeded. */
+int fw_graph_from_edgelist(const char* path, int32_t n_labels, float weight_lo, float weight_hi,
+                           uint64_t seed, fw_graph** out);
 int fw_graph_info(const fw_graph* g, int64_t* V, int64_t* E, int32_t* xadj_bits,
                   int32_t* has_weight, int32_t* has_label);
 /* Borrowed pointers into the graph (valid until fw_graph_destroy). */

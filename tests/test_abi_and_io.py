@@ -121,3 +121,26 @@ def test_reads_the_reference_sample_graph():
     assert (g.V, g.E) == (7115, 201524)
     assert g.max_degree()[1] == 1065
     assert g.weight.min() > 0 and g.weight.max() < 5 and set(np.unique(g.label)) == {0, 1, 2, 3, 4}
+
+
+def test_edgelist_converter(tmp_path):
+    path = tmp_path / "toy.edgelist"
+    path.write_text("# a comment\n10 20\n20 10\n10 30\n30 30\n40 20\n% another\n20 40\n50 10\n")
+    g = fw.Graph.from_edgelist(str(path), n_labels=5, weight_range=(1.0, 5.0), seed=3)
+    # first appearance: 10->0, 20->1, 30->2, 40->3, 50->4; undirected edges {0-1, 0-2, 1-3, 0-4}
+    assert (g.V, g.E) == (5, 8)
+    xa = g.xadj.astype(np.int64)
+    rows = [g.adj[xa[v]:xa[v + 1]].tolist() for v in range(g.V)]
+    assert rows == [[1, 2, 4], [0, 3], [0], [1], [0]]
+    w = {(v, int(x)): float(g.weight[e]) for v in range(g.V) for e, x in zip(range(xa[v], xa[v + 1]), g.adj[xa[v]:xa[v + 1]])}
+    lab = {(v, int(x)): int(g.label[e]) for v in range(g.V) for e, x in zip(range(xa[v], xa[v + 1]), g.adj[xa[v]:xa[v + 1]])}
+    for (u, v), val in w.items():
+        assert w[(v, u)] == val and 1.0 <= val < 5.0 and lab[(v, u)] == lab[(u, v)] and 0 <= lab[(u, v)] < 5
+    again = fw.Graph.from_edgelist(str(path), n_labels=5, weight_range=(1.0, 5.0), seed=3)
+    assert (again.weight == g.weight).all() and (again.label == g.label).all()
+    with pytest.raises(fw.FlowWalkerError):
+        fw.Graph.from_edgelist(str(tmp_path / "missing.edgelist"))
+    bad = tmp_path / "bad.edgelist"
+    bad.write_text("1 2\nhello\n")
+    with pytest.raises(fw.FlowWalkerError):
+        fw.Graph.from_edgelist(str(bad))

@@ -34,6 +34,16 @@ def test_flag_errors_and_help():
     assert r.returncode == 1 and "cannot open" in r.stderr
 
 
+def test_convert_edgelist(tmp_path):
+    el = tmp_path / "t.edgelist"
+    el.write_text("1 2\n2 3\n3 1\n3 4\n")
+    prefix = str(tmp_path / "t")
+    r = run("--edgelist", str(el), "--save_csr", prefix)
+    assert r.returncode == 0, r.stdout + r.stderr
+    g = fw.Graph.load(prefix, True, True)
+    assert (g.V, g.E) == (4, 8) and g.adj[:2].tolist() == [1, 2]
+
+
 def test_needs_exactly_one_app(tmp_path):
     g = graphs.config1()
     prefix = str(tmp_path / "g")
