@@ -7,6 +7,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 APP_DEEPWALK, APP_PPR, APP_NODE2VEC, APP_METAPATH = 0, 1, 2, 3
 GROUP_EDGE, GROUP_STRIP = 1, 64
+ENGINE_MANAGED = 4
 
 
 class FlowWalkerError(RuntimeError):
@@ -195,9 +196,9 @@ def rmat(scale, draws, a=0.57, b=0.19, c=0.19, seed=1, v_limit=0, e_target=0, we
 class Engine:
     """Device replica of a graph on one GPU (fw_engine)."""
 
-    def __init__(self, graph, device=0, which=0):
+    def __init__(self, graph, device=0, which=0, managed=False):
         self._h = ctypes.c_void_p()
-        _check(lib().fw_engine_create(graph._h, device, which, self._h))
+        _check(lib().fw_engine_create(graph._h, device, which | (ENGINE_MANAGED if managed else 0), self._h))
         dev, sms = ctypes.c_int(), ctypes.c_int()
         _check(lib().fw_engine_device(self._h, dev, sms))
         self.device, self.sm_count = dev.value, sms.value

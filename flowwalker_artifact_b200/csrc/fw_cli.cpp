@@ -28,7 +28,7 @@ void define_flags(fwflags::Parser& fl) {
   fl.add("seq", Flag::kBool, "false", "start from 0 to n-1");
   fl.add("all", Flag::kBool, "false", "start from all nodes");
   fl.add("d", Flag::kInt, "80", "depth");
-  fl.add("umgraph", Flag::kBool, "false", "accepted for compatibility (the graph always lives in device memory)");
+  fl.add("umgraph", Flag::kBool, "false", "edge arrays in unified memory (graphs larger than device memory)");
   fl.add("deepwalk", Flag::kBool, "false", "deepwalk");
   fl.add("node2vec", Flag::kBool, "false", "node2vec");
   fl.add("ppr", Flag::kBool, "false", "ppr");
@@ -251,7 +251,7 @@ int main(int argc, char** argv) {
   std::vector<std::string> errs((size_t)gpus);
   std::vector<fw_engine*> engines((size_t)gpus, nullptr);
   for (int r = 0; r < gpus; ++r)
-    if (fw_engine_create(g, r, 0, &engines[(size_t)r]) != FW_OK) return fail("engine");
+    if (fw_engine_create(g, r, fl.b("umgraph") ? FW_ENGINE_MANAGED : 0, &engines[(size_t)r]) != FW_OK) return fail("engine");
   const auto t0 = std::chrono::steady_clock::now();
   std::vector<std::thread> threads;
   for (int r = 0; r < gpus; ++r) {

@@ -77,11 +77,27 @@ struct DeviceGuard {
 // Edge arrays are padded to whole quads (plus one) so that 16-byte loads of
 // the first and last quad of any row stay inside the allocation.
 template <typename T>
-int upload_edges(const T* host, int64_t E, T** out) {
+int upload_edges(const T* host, int64_t E, T** out, int device, bool managed) {
   const size_t padded = ((size_t)E + 3) / 4 * 4 + 4;
-  FW_CUDA(cudaMalloc(out, padded * sizeof(T)));
-  FW_CUDA(cudaMemset(*out, 0, padded * sizeof(T)));
+  if (managed) {
+    // Unified memory (the role of --umgraph, include/gpu_graph.cuh:46-54): the array may exceed
+    // the device's memory; pages live on the device as far as they fit and migrate on demand.
+    FW_CUDA(cudaMallocManaged(out, padded * sizeof(T)));
+    FW_CUDA(cudaMemAdvise(*out, padded * sizeof(T), cudaMemAdviseSetPreferredLocation, device));
+  } else {
+    FW_CUDA(cudaMalloc(out, padded * sizeof(T)));
+  }
+  const size_t tail = (size_t)E / 4 * 4;  // the padding, and the last partial quad, start at zero
+  FW_CUDA(cudaMemset(*out + tail, 0, (padded - tail) * sizeof(T)));
   if (E > 0) FW_CUDA(cudaMemcpy(*out, host, (size_t)E * sizeof(T), cudaMemcpyHostToDevice));
+  if (managed) {
+    size_t free_b = 0, total_b = 0;
+    FW_CUDA(cudaMemGetInfo(&free_b, &total_b));
+    const size_t keep = (size_t)1 << 30;  // leave room for results and the other arrays' share
+    const size_t fit = free_b > keep ? std::min(padded * sizeof(T), free_b - keep) : 0;
+    if (fit) FW_CUDA(cudaMemPrefetchAsync(*out, fit, device, 0));
+    FW_CUDA(cudaDeviceSynchronize());
+  }
   return FW_OK;
 }
 
@@ -211,6 +227,9 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
   if (!e) return fw::fail(FW_ERR_NOMEM, "out of host memory");
   e->device = device; e->sms = prop.multiProcessorCount;
   e->V = g->V; e->E = g->E; e->xadj_bits = g->xadj_bits;
+  const bool managed = (which & FW_ENGINE_MANAGED) != 0;
+  which &= ~FW_ENGINE_MANAGED;
+  if (which < 0 || which > 3) { delete e; return fw::fail(FW_ERR_ARG, "fw_engine_create: unknown bits in `which`"); }
   const bool want_w = which == 0 ? g->weight != nullptr : (which & 1) != 0;
   const bool want_l = which == 0 ? g->label != nullptr : (which & 2) != 0;
   int rc = FW_OK;
@@ -222,14 +241,14 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
     const size_t xb = (size_t)(g->xadj_bits / 8) * (size_t)(g->V + 2);
     FW_CUDA(cudaMalloc(&e->d_xadj, xb));
     FW_CUDA(cudaMemcpy(e->d_xadj, g->xadj, (size_t)(g->xadj_bits / 8) * (size_t)(g->V + 1), cudaMemcpyHostToDevice));
-    int r = upload_edges(g->adj, g->E, &e->d_adj);
-    if (!r && want_w) r = upload_edges(g->weight, g->E, &e->d_weight);
+    int r = upload_edges(g->adj, g->E, &e->d_adj, device, managed);
+    if (!r && want_w) r = upload_edges(g->weight, g->E, &e->d_weight, device, managed);
     if (want_w) {
       bool clean = true;
       for (int64_t i = 0; i < g->E && clean; ++i) clean = g->weight[i] >= 0.0f;
       e->clean_weights = clean;
     }
-    if (!r && want_l) r = upload_edges(g->label, g->E, &e->d_label);
+    if (!r && want_l) r = upload_edges(g->label, g->E, &e->d_label, device, managed);
     if (r) return r;
     FW_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
     FW_CUDA(cudaStreamCreateWithFlags(&e->stream2, cudaStreamNonBlocking));

@@ -127,8 +127,11 @@ void fw_graph_destroy(fw_graph* g);
 
 /* ---- engine: gpu_graph construction (include/gpu_graph.cuh:39-78) ---- */
 
-/* Uploads (replicates) the graph to `device`.  which: bit 0 = weights, bit 1 = labels;
- * 0 uploads whatever the graph has. */
+/* Uploads (replicates) the graph to `device`.  which: bit 0 = weights, bit 1 = labels; neither
+ * bit uploads whatever the graph has.  FW_ENGINE_MANAGED (bit 2) puts the edge arrays in unified
+ * memory (the role of --umgraph, include/gpu_graph.cuh:46-54): they may then exceed the device's
+ * memory, live on the device as far as they fit and migrate on demand. */
+#define FW_ENGINE_MANAGED 4
 int fw_engine_create(const fw_graph* g, int device, int which, fw_engine** out);
 void fw_engine_destroy(fw_engine* e);
 int fw_engine_device(const fw_engine* e, int* device, int* sm_count);

@@ -57,6 +57,7 @@ def test_needs_exactly_one_app(tmp_path):
     (fw.APP_DEEPWALK, ["--deepwalk", "--d=20"], dict(d=20)),
     (fw.APP_NODE2VEC, ["--node2vec", "--d", "20", "--p=0.5", "--q", "2"], dict(d=20, p=0.5, q=2.0)),
     (fw.APP_METAPATH, ["--metapath", "--schema=1,2,3"], dict(d=3, schema=[1, 2, 3])),
+    (fw.APP_PPR, ["--ppr", "--tp=0.1", "--umgraph"], dict(d=80, tp=0.1)),
 ])
 def test_cli_walks_match_the_golden_walker(tmp_path, app, flags, kw):
     g = graphs.config1()

@@ -17,9 +17,9 @@ APPS = [
 MODES = [fw.GROUP_STRIP, fw.GROUP_EDGE]
 
 
-def run_both(arrs, app, kw, starts, mode, seed=1337, base=0, sharing=-1):
+def run_both(arrs, app, kw, starts, mode, seed=1337, base=0, sharing=-1, managed=False):
     g = fw.Graph.from_arrays(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"])
-    eng = fw.Engine(g, 0)
+    eng = fw.Engine(g, 0, managed=managed)
     eng.set_sharing(sharing)
     prm = fw.make_params(app, group_mode=mode, seed=seed, query_id_base=base, **kw)
     res, st, hist = eng.walk(prm, starts, want_hist=True)
@@ -146,3 +146,57 @@ def test_bounded_wait_reports_instead_of_hanging():
     g = graphs.config1()
     arrs = dict(xadj=g.xadj.copy(), adj=g.adj.copy(), weight=g.weight.copy(), label=g.label.copy())
     assert_same(run_both(arrs, fw.APP_DEEPWALK, dict(d=20), graphs.config1_starts(), fw.GROUP_STRIP))
+
+
+def _threshold_graph(rng, case):
+    """Rows whose lengths sit around every dispatch threshold of the kernel; the other vertices
+    are three-neighbour rows that lead back into them."""
+    V = 9000
+    marks = [1, 2, 5, 31, 32, 33, 120, 127, 128, 129, 131, 255, 256, 257, 500, 511, 512, 513, 1023, 1025,
+             2047, 2048, 2049, 2100, 4095, 4096, 4100, 6000, 8191, 8200]
+    degs = [int(rng.choice(marks)) for _ in range(300)] + [0] * 5
+    if case % 3 == 0:
+        degs += [8999, 7000]
+    rng.shuffle(degs)
+    n_rows = len(degs)
+    rows = []
+    for dg in degs:
+        if case % 2 == 1:  # parallel edges, and rows that share many neighbours
+            rows.append(np.sort(rng.integers(0, 4 * n_rows, size=dg)))
+        else:
+            rows.append(np.sort(rng.choice(V, size=dg, replace=False)))
+    for v in range(n_rows, V):
+        rows.append(np.sort(rng.choice(n_rows, size=3, replace=False)))
+    g = graphs.from_rows(rows, V=V, rng=rng, weight_range=(0.05, 3.0),
+                         xadj_dtype=np.uint32 if case % 2 else np.int64)
+    if case % 4 >= 2:  # zero and negative weights
+        idx = rng.choice(len(g["weight"]), size=len(g["weight"]) // 7, replace=False)
+        g["weight"][idx[::2]] = 0.0
+        g["weight"][idx[1::2]] = -2.0
+    return g, n_rows
+
+
+@pytest.mark.parametrize("case", range(10))
+def test_random_graphs_all_apps(case):
+    """Seeded random graphs: row lengths around 32 quads, two and three sub-blocks, one and several
+    supergroups; parallel edges; zero and negative weights; p and q on both sides of 1; several
+    stop probabilities and schemas; both offset widths; sharing on and off."""
+    rng = np.random.default_rng(1000 + case)
+    arrs, n_rows = _threshold_graph(rng, case)
+    starts = rng.integers(0, n_rows, 600).astype(np.int32)
+    p, q = [(2.0, 0.5), (0.25, 4.0), (1.0, 1.0), (0.5, 3.0), (4.0, 0.25)][case % 5]
+    cases = [(fw.APP_DEEPWALK, dict(d=9)), (fw.APP_PPR, dict(d=30, tp=[0.05, 0.2, 0.6][case % 3])),
+             (fw.APP_NODE2VEC, dict(d=9, p=p, q=q)),
+             (fw.APP_METAPATH, dict(d=6, schema=[[0, 1, 2, 3, 4], [2, 2, 0], [4]][case % 3]))]
+    for app, kw in cases:
+        for mode in ((fw.GROUP_STRIP, fw.GROUP_EDGE) if case < 4 else (fw.GROUP_STRIP,)):
+            assert_same(run_both(arrs, app, kw, starts, mode, seed=31 + case, base=case * 10 ** 6,
+                                 sharing=case % 2))
+
+
+@pytest.mark.parametrize("app,kw", APPS)
+def test_managed_graph(app, kw):
+    """Edge arrays in unified memory (--umgraph): same walks."""
+    arrs = graphs.ragged()
+    starts = np.arange(arrs["n_rows"], dtype=np.int32)
+    assert_same(run_both(arrs, app, kw, starts, fw.GROUP_STRIP, managed=True))
