@@ -200,3 +200,39 @@ def test_managed_graph(app, kw):
     arrs = graphs.ragged()
     starts = np.arange(arrs["n_rows"], dtype=np.int32)
     assert_same(run_both(arrs, app, kw, starts, fw.GROUP_STRIP, managed=True))
+
+
+def test_host_threads_share_an_engine():
+    """Calls on one engine from several host threads are serialised by the library; calls on two
+    engines of the same device run side by side.  Every thread gets the single-thread walks."""
+    import threading
+    g = graphs.config1()
+    starts = np.arange(g.V, dtype=np.int32)
+    engines = [fw.Engine(g, 0), fw.Engine(g, 0)]
+    prms = [fw.make_params(fw.APP_DEEPWALK, d=40, seed=5), fw.make_params(fw.APP_PPR, d=80, tp=0.2, seed=6),
+            fw.make_params(fw.APP_NODE2VEC, d=30, p=2.0, q=0.5, seed=7)]
+    expect = [engines[0].walk(p, starts)[0] for p in prms]
+    got, errors = {}, []
+
+    def work(tid):
+        try:
+            for rep in range(4):
+                k = (tid + rep) % len(prms)
+                res, st = engines[tid % 2].walk(prms[k], starts)
+                assert st.device_status == 0
+                got[(tid, rep)] = (k, res)
+        except Exception as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(t,)) for t in range(6)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert len(got) == 24
+    for k, res in got.values():
+        assert (res == expect[k]).all()
+    for e in engines:
+        e.close()
+    g.close()
