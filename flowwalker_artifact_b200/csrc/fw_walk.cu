@@ -174,8 +174,10 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   return FW_OK;
 }
 
-void collect(const unsigned long long* h, int d, float ms, int launches, fw_walk_stats* stats,
-             uint64_t* len_hist, bool accumulate) {
+// Returns FW_ERR_DEVICE when the kernel gave up on a bounded wait (the walks of that launch are
+// incomplete); bad start or neighbour ids only set their status bits.
+int collect(const unsigned long long* h, int d, float ms, int launches, fw_walk_stats* stats,
+            uint64_t* len_hist, bool accumulate) {
   if (stats) {
     if (!accumulate) { stats->steps = 0; stats->scanned = 0; stats->device_ms = 0; stats->device_status = 0; stats->launches = 0; }
     stats->steps += h[kSlotSteps];
@@ -186,6 +188,9 @@ void collect(const unsigned long long* h, int d, float ms, int launches, fw_walk
   }
   if (len_hist)
     for (int z = 0; z <= d; ++z) len_hist[z] = (accumulate ? len_hist[z] : 0) + h[kSlotHist + z];
+  if (h[kSlotStatus] & FW_STATUS_WAIT_TIMEOUT)
+    return fw::fail(FW_ERR_DEVICE, "the walk kernel gave up waiting for a staged copy; the result is incomplete");
+  return FW_OK;
 }
 
 template <typename T>
@@ -304,9 +309,9 @@ extern "C" int fw_walk_device(fw_engine* e, const fw_walk_params* p, const int32
   FW_CUDA(cudaStreamSynchronize(st));
   float ms = 0.f;
   FW_CUDA(cudaEventElapsedTime(&ms, e->ev[0], e->ev[1]));
-  collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
+  rc = collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
   if (stats) stats->total_ms = ms;
-  return FW_OK;
+  return rc;
 }
 
 extern "C" int fw_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_host, int64_t n,
@@ -334,9 +339,9 @@ extern "C" int fw_walk(fw_engine* e, const fw_walk_params* p, const int32_t* sta
   float ms = 0.f, total = 0.f;
   FW_CUDA(cudaEventElapsedTime(&ms, e->ev[0], e->ev[1]));
   FW_CUDA(cudaEventElapsedTime(&total, e->ev[2], e->ev[3]));
-  collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
+  rc = collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
   if (stats) stats->total_ms = total;
-  return FW_OK;
+  return rc;
 }
 
 extern "C" void fw_free_pinned(void* p) {
@@ -386,9 +391,8 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
     FW_CUDA(cudaStreamSynchronize(streams[s]));
     float ms = 0.f;
     FW_CUDA(cudaEventElapsedTime(&ms, evs[s][0], evs[s][1]));
-    collect(hsc[s], p->d, ms, 1, stats, len_hist, true);
     pending[s] = false;
-    return FW_OK;
+    return collect(hsc[s], p->d, ms, 1, stats, len_hist, true);
   };
   int which = 0;
   fw_walk_params bp = *p;
@@ -607,5 +611,7 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
     stats->total_ms = 0.0;
     stats->launches = n > 0 ? 1 : 0;
   }
+  if (head[kSlotStatus] & FW_STATUS_WAIT_TIMEOUT)
+    return fw::fail(FW_ERR_DEVICE, "the walk kernel gave up waiting for a staged copy; the result is incomplete");
   return FW_OK;
 }

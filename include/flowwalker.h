@@ -29,7 +29,7 @@ extern "C" {
 #define FW_ERR_IO (-2)      /* missing / truncated / inconsistent file */
 #define FW_ERR_CUDA (-3)    /* a CUDA runtime call failed */
 #define FW_ERR_NOMEM (-4)   /* host or device allocation failed */
-#define FW_ERR_DEVICE (-5)  /* the kernel reported an error status */
+#define FW_ERR_DEVICE (-5)  /* the kernel gave up on a bounded wait (FW_STATUS_WAIT_TIMEOUT): result incomplete */
 
 /* Applications: include/app.cuh:58-152 (Deepwalk, PPR, Node2vec, Metapath). */
 #define FW_APP_DEEPWALK 0
