@@ -255,29 +255,42 @@ __device__ __forceinline__ uint32_t n2v_linked(const WalkArgs& a, const StepCtx&
 // neighbour ids and `linked`, which of them are adjacent to the previous vertex: node2vec
 // only).  Edges outside the row are NOT masked here.
 // CLEAN: the weights are known to be >= 0 and not NaN, so the clamp is skipped.
+// Plain edge weights inside the node2vec kernels (their sweep of upper bounds, their first
+// step): the same bias as DeepWalk, but through the compact code with one path per block.
+// Those kernels are the largest and were measured 13 % slower with the two-path blocks.
+constexpr int kAppPlainCompact = 16;
+
+template <int APP, bool CLEAN>
+__device__ __forceinline__ float4 plain_bias(int4 raw, int32_t want) {
+  float4 v;
+  if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
+    v.x = raw.x == want ? 1.0f : 0.0f;
+    v.y = raw.y == want ? 1.0f : 0.0f;
+    v.z = raw.z == want ? 1.0f : 0.0f;
+    v.w = raw.w == want ? 1.0f : 0.0f;
+  } else {
+    v = make_float4(__int_as_float(raw.x), __int_as_float(raw.y), __int_as_float(raw.z), __int_as_float(raw.w));
+    if (!CLEAN) { v.x = pos(v.x); v.y = pos(v.y); v.z = pos(v.z); v.w = pos(v.w); }
+  }
+  return v;
+}
+
 template <int APP, bool CLEAN>
 __device__ __forceinline__ float4 quad_bias(const WalkArgs& a, const StepCtx& c, int4 raw, int4 nb, uint32_t q,
                                             uint32_t linked = 0u) {
-  float4 v;
-  if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
-    v.x = raw.x == c.want ? 1.0f : 0.0f;
-    v.y = raw.y == c.want ? 1.0f : 0.0f;
-    v.z = raw.z == c.want ? 1.0f : 0.0f;
-    v.w = raw.w == c.want ? 1.0f : 0.0f;
-  } else {
-    v = make_float4(__int_as_float(raw.x), __int_as_float(raw.y), __int_as_float(raw.z), __int_as_float(raw.w));
-    if (APP == FW_APP_NODE2VEC && c.prev >= 0) {  // include/app.cuh:109-122
-      const int32_t xs[4] = {nb.x, nb.y, nb.z, nb.w};
-      float vs[4] = {v.x, v.y, v.z, v.w};
+  if (APP != FW_APP_NODE2VEC) return plain_bias<APP, CLEAN>(raw, c.want);
+  float4 v = make_float4(__int_as_float(raw.x), __int_as_float(raw.y), __int_as_float(raw.z), __int_as_float(raw.w));
+  if (c.prev >= 0) {  // include/app.cuh:109-122
+    const int32_t xs[4] = {nb.x, nb.y, nb.z, nb.w};
+    float vs[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {  // edges outside the row are zeroed by the caller's mask
-        if (xs[k] == c.prev) vs[k] = __fmul_rn(vs[k], a.inv_p);
-        else if (!((linked >> k) & 1u)) vs[k] = __fmul_rn(vs[k], a.inv_q);
-      }
-      v = make_float4(vs[0], vs[1], vs[2], vs[3]);
+    for (int k = 0; k < 4; ++k) {  // edges outside the row are zeroed by the caller's mask
+      if (xs[k] == c.prev) vs[k] = __fmul_rn(vs[k], a.inv_p);
+      else if (!((linked >> k) & 1u)) vs[k] = __fmul_rn(vs[k], a.inv_q);
     }
-    if (!CLEAN) { v.x = pos(v.x); v.y = pos(v.y); v.z = pos(v.z); v.w = pos(v.w); }
+    v = make_float4(vs[0], vs[1], vs[2], vs[3]);
   }
+  if (!CLEAN) { v.x = pos(v.x); v.y = pos(v.y); v.z = pos(v.z); v.w = pos(v.w); }
   return v;
 }
 
@@ -312,6 +325,27 @@ __device__ __forceinline__ float4 load_quad(const WalkArgs& a, const StepCtx& c,
   return v;
 }
 
+// Quad 32 blk + l of the row, blk <= last_blk (warp-uniform; every lane of the warp calls this).
+// Only the row's first and last block can hold a quad that is cut by the row bounds or lies
+// past the end; the blocks in between run without bounds tests or masks.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ float4 block_quad(const WalkArgs& a, const StepCtx& c, uint32_t blk, uint32_t last_blk,
+                                             uint32_t l) {
+  if (APP == FW_APP_NODE2VEC || APP == kAppPlainCompact)
+    return load_quad<APP, CLEAN>(a, c, 32u * blk + l, blk == 0u || blk == last_blk);
+  const uint32_t q = 32u * blk + l;
+  if (blk != 0u && blk < last_blk) return plain_bias<APP, CLEAN>(__ldg(c.prim + q), c.want);
+  // The warp-level barrier is there for the compiler: without it the two paths are folded into
+  // one load followed by the masks, and every interior block pays for them again.
+  __syncwarp();
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (q < c.nq) {
+    v = plain_bias<APP, CLEAN>(__ldg(c.prim + q), c.want);
+    mask_quad(v, q, c.head, c.tail);
+  }
+  return v;
+}
+
 // Lane `lane`'s four quads of sub-block b (quads 128 b + 32 j + lane, j = 0..3) from global
 // memory: their total bias in the fixed order (S0+S1)+(S2+S3).  Blocks of 32 quads past the
 // end of the row are skipped as a warp.
@@ -322,10 +356,22 @@ __device__ __forceinline__ float sub_global(const WalkArgs& a, const StepCtx& c,
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint32_t blk = 4u * b + j;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (blk <= last_blk) v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, blk == 0u || blk == last_blk);
-    S[j] = sum4(v);
+    S[j] = 0.0f;
+    if (blk <= last_blk) S[j] = sum4(block_quad<APP, CLEAN>(a, c, blk, last_blk, lane));
   }
+  return sum_strip(S);
+}
+
+// Sub-block 0 of a row of more than 32 quads.  `more` (warp-uniform): the row has further
+// sub-blocks, so blocks 1..3 are interior and need no test at all.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ float sub_first(const WalkArgs& a, const StepCtx& c, bool more, uint32_t lane) {
+  if (APP == FW_APP_NODE2VEC || APP == kAppPlainCompact || !more) return sub_global<APP, CLEAN>(a, c, 0u, lane);
+  const uint32_t last_blk = (c.nq - 1u) >> 5;
+  float S[4];
+  S[0] = sum4(block_quad<APP, CLEAN>(a, c, 0u, last_blk, lane));
+#pragma unroll
+  for (int j = 1; j < 4; ++j) S[j] = sum4(plain_bias<APP, CLEAN>(__ldg(c.prim + (32u * j + lane)), c.want));
   return sum_strip(S);
 }
 
@@ -531,7 +577,7 @@ __device__ __forceinline__ uint32_t n2v_pick(const WalkArgs& a, const StepCtx& c
 
 // The sweep of node2vec reads plain weights (DeepWalk's bias); its own bias enters per strip.
 template <int APP>
-struct SweepApp { static constexpr int value = APP == FW_APP_NODE2VEC ? FW_APP_DEEPWALK : APP; };
+struct SweepApp { static constexpr int value = APP == FW_APP_NODE2VEC ? kAppPlainCompact : APP; };
 
 // A lane's running state while a row is swept: the partial sums of the current supergroup
 // and the Philox block that serves it.
@@ -592,13 +638,15 @@ __device__ __forceinline__ uint32_t pick_in_row(const WalkArgs& a, const StepCtx
       v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
       v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
     } else {
-      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
+      v = block_quad<APP, CLEAN>(a, c, blk, last_blk, lB);
     }
-    acc = __fadd_rn(acc, v.x); cnt += acc <= thr ? 1u : 0u;
-    acc = __fadd_rn(acc, v.y); cnt += acc <= thr ? 1u : 0u;
-    acc = __fadd_rn(acc, v.z); cnt += acc <= thr ? 1u : 0u;
-    acc = __fadd_rn(acc, v.w); cnt += acc <= thr ? 1u : 0u;
-    if (cnt < 4u * (j + 1u)) break;  // found (warp-uniform)
+    // biases are >= 0, so the running sums never decrease: when the quad's last sum is still
+    // <= thr all four are, and the quad is passed with one comparison
+    const float p0 = __fadd_rn(acc, v.x), p1 = __fadd_rn(p0, v.y), p2 = __fadd_rn(p1, v.z);
+    acc = __fadd_rn(p2, v.w);
+    if (acc <= thr) { cnt += 4u; continue; }
+    cnt += (p0 <= thr ? 1u : 0u) + (p1 <= thr ? 1u : 0u) + (p2 <= thr ? 1u : 0u);
+    break;  // found (warp-uniform)
   }
   if (j == nblk) {
     // rounding pushed u * W past the sequential total: take the strip's last positive edge
@@ -616,7 +664,7 @@ __device__ __forceinline__ uint32_t pick_in_row(const WalkArgs& a, const StepCtx
         v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
         v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
       } else {
-        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lB, edge_blk);
+        v = block_quad<APP, CLEAN>(a, c, blk, last_blk, lB);
       }
       if (v.x > 0.0f) cnt = 4u * j;
       if (v.y > 0.0f) cnt = 4u * j + 1u;
@@ -920,7 +968,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     if (lane == 0) k = ld_volatile(&task->ticket) & 0xFFFFu;
     return (b >> 2) + __shfl_sync(0xFFFFFFFFu, k, 0) * kCoopChunkSupers >= end_super;
   };
-  absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, 0u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
+  absorb<APP, CLEAN>(a, c, acc, best, sub_first<SweepApp<APP>::value, CLEAN>(a, c, nb > 1u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
   uint32_t b = 1;
   if (!ringed) {
 #pragma unroll 1
