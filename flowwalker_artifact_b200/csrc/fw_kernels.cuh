@@ -59,6 +59,7 @@ struct WalkArgs {
   float inv_p, inv_q;
   float n2v_fmax;  // node2vec: max(1, 1/p, 1/q) with a margin of 1e-5 for rounding
   uint32_t k0, k1;
+  uint32_t rk[20];  // the Philox round keys of (k0, k1): fw::philox_round_keys
   int32_t hist_in_smem;
   int32_t schema_len;
   int32_t schema[kMaxSchema];
@@ -902,7 +903,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
       if (APP == FW_APP_NODE2VEC && c.prev >= 0) linked = n2v_linked(a, c, nb, q, true, lane);
       float4 v = quad_bias<APP, CLEAN>(a, c, raw, nb, q, linked);
       mask_quad(v, q, c.head, c.tail);
-      const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.k0, a.k1);
+      const fw::Philox4 r = fw::philox4x32_10(q, c1, qlo, qhi, a.rk);
       const float vs[4] = {v.x, v.y, v.z, v.w};
       const uint32_t rs[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -922,7 +923,10 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   // 0 = g*32 + l) serves supergroups 3g, 3g+1, 3g+2 (words 0..2 -> keys) and carries in
   // word 3 the uniform for the in-strip pick.
   Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
-  fw::Philox4 r = fw::philox4x32_10(lane, c1, qlo, qhi, a.k0, a.k1);
+  // round keys straight from the kernel arguments; the node2vec kernels, short of registers,
+  // measured faster with the key schedule computed in place
+  fw::Philox4 r = APP == FW_APP_NODE2VEC ? fw::philox4x32_10(lane, c1, qlo, qhi, a.k0, a.k1)
+                                         : fw::philox4x32_10(lane, c1, qlo, qhi, a.rk);
 
   if (c.nq <= 32u) {
     // Short row: one quad per lane, strip = that quad; the winner's quad travels by shuffle.
@@ -1037,7 +1041,16 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
-__global__ void __launch_bounds__(kThreads, MODE != FW_GROUP_EDGE && APP != FW_APP_NODE2VEC ? FW_MIN_BLOCKS : (MODE != FW_GROUP_EDGE ? FW_N2V_MIN_BLOCKS : 2)) walk_kernel(const __grid_constant__ WalkArgs a) {
+constexpr int min_blocks() {
+  // Six CTAs of 256 threads per SM need at most 40 registers per thread.  DeepWalk and PPR fit
+  // by themselves; small source changes move the 32-bit MetaPath kernel between 38 and 45, so
+  // it is held to the limit; 64-bit offsets and node2vec need more registers.
+  return MODE == FW_GROUP_EDGE ? 2 : APP == FW_APP_NODE2VEC ? FW_N2V_MIN_BLOCKS
+       : (APP == FW_APP_METAPATH && MODE == FW_GROUP_STRIP && sizeof(OffT) == 4) ? 6 : FW_MIN_BLOCKS;
+}
+
+template <int APP, int MODE, bool CLEAN, typename OffT>
+__global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()) walk_kernel(const __grid_constant__ WalkArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
@@ -1112,7 +1125,7 @@ __global__ void __launch_bounds__(kThreads, MODE != FW_GROUP_EDGE && APP != FW_A
           ++k;
           if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
             const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(k - 1) | (fw::kPurposeStop << 28),
-                                                    qlo, qhi, a.k0, a.k1);
+                                                    qlo, qhi, a.rk);
             if (r.x < a.tp_thresh) break;
           }
         }

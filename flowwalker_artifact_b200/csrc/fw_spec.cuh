@@ -55,6 +55,33 @@ FW_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
   return Philox4{c0, c1, c2, c3};
 }
 
+// The same function with the ten round keys formed ahead of time: rk[2r] = k0 + r * 0x9E3779B9,
+// rk[2r+1] = k1 + r * 0xBB67AE85 (mod 2^32).  A kernel that keeps them among its arguments
+// reads each straight from the constant bank and saves the key schedule of every call.
+FW_HD void philox_round_keys(uint32_t k0, uint32_t k1, uint32_t rk[20]) {
+  for (int r = 0; r < 10; ++r) {
+    rk[2 * r] = k0;
+    rk[2 * r + 1] = k1;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+
+FW_HD Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const uint32_t (&rk)[20]) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ rk[2 * r];
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ rk[2 * r + 1];
+    c1 = (uint32_t)p1;
+    c3 = (uint32_t)p0;
+    c0 = n0;
+    c2 = n2;
+  }
+  return Philox4{c0, c1, c2, c3};
+}
+
 FW_HD int clz32(uint32_t x) {
 #if defined(__CUDA_ARCH__)
   return __clz((int)x);

@@ -145,6 +145,7 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   a.inv_p = (float)(1.0 / p->p); a.inv_q = (float)(1.0 / p->q);
   a.n2v_fmax = std::max(1.0f, std::max(a.inv_p, a.inv_q)) * 1.00001f;
   a.k0 = (uint32_t)p->seed; a.k1 = (uint32_t)(p->seed >> 32);
+  fw::philox_round_keys(a.k0, a.k1, a.rk);
   a.hist_in_smem = p->d + 1 <= kMaxSmemHist;
   a.schema_len = p->app == FW_APP_METAPATH ? p->schema_len : 1;
   for (int i = 0; i < kMaxSchema; ++i) a.schema[i] = (p->app == FW_APP_METAPATH && i < p->schema_len) ? p->schema[i] : 0;
@@ -575,6 +576,7 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
   a.inv_p = (float)(1.0 / p->p); a.inv_q = (float)(1.0 / p->q);
   a.n2v_fmax = std::max(1.0f, std::max(a.inv_p, a.inv_q)) * 1.00001f;
   a.k0 = (uint32_t)p->seed; a.k1 = (uint32_t)(p->seed >> 32);
+  fw::philox_round_keys(a.k0, a.k1, a.rk);
   a.hist_in_smem = 1;  // d + 1 <= 4096 words always fits
   a.schema_len = p->app == FW_APP_METAPATH ? p->schema_len : 1;
   for (int i = 0; i < kMaxSchema; ++i)

@@ -1,8 +1,9 @@
 """Cross-check against the reference's own CUDA walker (unmodified sources rebuilt for sm_100
 by oracle/build_ref.sh into oracle/_ref/ref_walk) on the same graph and start vertices:
 its per-vertex transition frequencies and ours must both follow each app's exact weighted
-transition law (chi-square, p > 0.001), and the walk-length distributions must agree within
-3 sigma.  The reference is not reproducible run to run, so nothing here is bit-exact."""
+transition law (chi-square, p > 0.001), and the walk-length distributions must agree (per-bin
+z-scores, mean within 4 sigma).  The reference is not reproducible run to run, so nothing here
+is bit-exact."""
 import json
 import os
 import subprocess
@@ -81,4 +82,7 @@ def test_same_law_as_reference(tmp_path, name, app, kw, n):
     big = (ha + hb) >= 20
     z = (ha[big] - hb[big]) / keep / sigma[big]
     assert np.abs(z).max() < 4.5 and (np.abs(z) > 3.0).mean() < 0.05, (name, z)
-    assert abs(la.mean() - lb.mean()) < 3.0 * np.sqrt((la.var() + lb.var()) / keep) + 1e-9
+    # the reference's walks differ from run to run, so this is a fresh draw every time: 4 sigma
+    # (6e-5 two-sided) keeps a sound pair from failing once in a few hundred runs, as 3 sigma did,
+    # while a 2 % shift of the mean length would still be a 6 sigma event
+    assert abs(la.mean() - lb.mean()) < 4.0 * np.sqrt((la.var() + lb.var()) / keep) + 1e-9
