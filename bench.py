@@ -41,7 +41,10 @@ def parse():
     ap.add_argument("--edge-factor", type=int, default=16)
     ap.add_argument("--d", type=int, default=80)
     ap.add_argument("--group", type=int, default=0, help="sampler granularity: 0 default, 1 or 64")
-    ap.add_argument("--queries", type=int, default=0, help="0 = all vertices")
+    ap.add_argument("--queries", type=int, default=0, help="0 = all vertices; otherwise seeded uniform starts")
+    ap.add_argument("--rmat-a", type=float, default=0.57, help="R-MAT a (b = c = 0.19)")
+    ap.add_argument("--weights", default="0,1", help="weights uniform in [lo,hi)")
+    ap.add_argument("--xadj-bits", type=int, default=32, choices=[32, 64])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -150,8 +153,16 @@ def cpu_baseline(g, args, budget_s=12.0, full=False):
 
 
 def workload_name(args):
-    return "%s --all d=%d on R-MAT scale-%d ef%d (a=.57,b=.19,c=.19), f32 weights in [0,1), int32 CSR" % (
-        args.app, args.d, args.scale, args.edge_factor)
+    starts = "--all" if not args.queries else "%d uniform starts" % args.queries
+    return "%s %s d=%d on R-MAT scale-%d ef%d (a=%s,b=.19,c=.19), f32 weights in [%s), int%d CSR" % (
+        args.app, starts, args.d, args.scale, args.edge_factor, ("%.2f" % args.rmat_a).lstrip("0"),
+        args.weights, args.xadj_bits)
+
+
+def make_graph(fw, args, device):
+    lo, hi = (float(x) for x in args.weights.split(","))
+    return fw.rmat(args.scale, args.edge_factor << args.scale, a=args.rmat_a, weight_range=(lo, hi),
+                   n_labels=5 if args.app == "metapath" else 0, xadj_bits=args.xadj_bits, device=device)
 
 
 def run_reference(args):
@@ -168,8 +179,7 @@ def run_reference(args):
     import tempfile
     import flowwalker_artifact_b200 as fw
     have_gpu = _has_cuda()
-    g = fw.rmat(args.scale, args.edge_factor << args.scale, n_labels=5 if args.app == "metapath" else 0,
-                device=0 if have_gpu else -1)
+    g = make_graph(fw, args, 0 if have_gpu else -1)
     ref_bin = os.path.join(ROOT, "oracle", "_ref", "ref_walk")
     line = {"impl": "reference", "metric": "walk steps/sec", "unit": "walk steps/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
@@ -251,8 +261,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    g = fw.rmat(args.scale, args.edge_factor << args.scale, n_labels=5 if args.app == "metapath" else 0,
-                device=local)
+    g = make_graph(fw, args, local)
     eng = fw.Engine(g, local)
     V = g.V
     n = args.queries or V

@@ -256,15 +256,17 @@ __device__ __forceinline__ uint32_t n2v_linked(const WalkArgs& a, const StepCtx&
 // neighbour ids and `linked`, which of them are adjacent to the previous vertex: node2vec
 // only).  Edges outside the row are NOT masked here.
 // CLEAN: the weights are known to be >= 0 and not NaN, so the clamp is skipped.
-// Plain edge weights inside the node2vec kernels (their sweep of upper bounds, their first
-// step): the same bias as DeepWalk, but through the compact code with one path per block.
-// Those kernels are the largest and were measured 13 % slower with the two-path blocks.
-constexpr int kAppPlainCompact = 16;
+// An app value with this bit set selects the compact form of the block code (one path per
+// block, the boundary masks folded into it) for the same bias.  The largest kernels use it --
+// node2vec (plain weights: its sweep of upper bounds, its first step) and the variants that
+// share rows between warps: they were measured 13 % and 30 % slower with the two-path blocks.
+constexpr int kCompact = 16;
+constexpr int kAppPlainCompact = FW_APP_DEEPWALK | kCompact;
 
 template <int APP, bool CLEAN>
 __device__ __forceinline__ float4 plain_bias(int4 raw, int32_t want) {
   float4 v;
-  if (APP == FW_APP_METAPATH) {  // include/app.cuh:142-147
+  if ((APP & (kCompact - 1)) == FW_APP_METAPATH) {  // include/app.cuh:142-147
     v.x = raw.x == want ? 1.0f : 0.0f;
     v.y = raw.y == want ? 1.0f : 0.0f;
     v.z = raw.z == want ? 1.0f : 0.0f;
@@ -332,7 +334,7 @@ __device__ __forceinline__ float4 load_quad(const WalkArgs& a, const StepCtx& c,
 template <int APP, bool CLEAN>
 __device__ __forceinline__ float4 block_quad(const WalkArgs& a, const StepCtx& c, uint32_t blk, uint32_t last_blk,
                                              uint32_t l) {
-  if (APP == FW_APP_NODE2VEC || APP == kAppPlainCompact)
+  if (APP == FW_APP_NODE2VEC || (APP & kCompact) != 0)
     return load_quad<APP, CLEAN>(a, c, 32u * blk + l, blk == 0u || blk == last_blk);
   const uint32_t q = 32u * blk + l;
   if (blk != 0u && blk < last_blk) return plain_bias<APP, CLEAN>(__ldg(c.prim + q), c.want);
@@ -367,7 +369,7 @@ __device__ __forceinline__ float sub_global(const WalkArgs& a, const StepCtx& c,
 // sub-blocks, so blocks 1..3 are interior and need no test at all.
 template <int APP, bool CLEAN>
 __device__ __forceinline__ float sub_first(const WalkArgs& a, const StepCtx& c, bool more, uint32_t lane) {
-  if (APP == FW_APP_NODE2VEC || APP == kAppPlainCompact || !more) return sub_global<APP, CLEAN>(a, c, 0u, lane);
+  if (APP == FW_APP_NODE2VEC || (APP & kCompact) != 0 || !more) return sub_global<APP, CLEAN>(a, c, 0u, lane);
   const uint32_t last_blk = (c.nq - 1u) >> 5;
   float S[4];
   S[0] = sum4(block_quad<APP, CLEAN>(a, c, 0u, last_blk, lane));
@@ -577,8 +579,16 @@ __device__ __forceinline__ uint32_t n2v_pick(const WalkArgs& a, const StepCtx& c
 }
 
 // The sweep of node2vec reads plain weights (DeepWalk's bias); its own bias enters per strip.
-template <int APP>
-struct SweepApp { static constexpr int value = APP == FW_APP_NODE2VEC ? kAppPlainCompact : APP; };
+// Kernel variant (template MODE) of the strip sampler whose warps also share very long rows: kept
+// apart because the sharing code costs the plain sweep registers (48 against 40, one CTA per SM less)
+// and about 20 % of its throughput; the engine selects it for graphs that have rows long enough to
+// leave a tail.
+constexpr int kModeStripShared = FW_GROUP_STRIP + 1;
+template <int APP, int MODE = kModeStripShared>
+struct SweepApp {
+  static constexpr int value = APP == FW_APP_NODE2VEC ? kAppPlainCompact
+                             : MODE == kModeStripShared ? (APP | kCompact) : APP;
+};
 
 // A lane's running state while a row is swept: the partial sums of the current supergroup
 // and the Philox block that serves it.
@@ -691,11 +701,6 @@ __device__ __forceinline__ uint32_t pick_in_row(const WalkArgs& a, const StepCtx
 // of the bulk phase.  Stands in for sampler_block (include/sampler.cuh:87-127) and the block
 // phase of the reference scheduler (include/walker.cuh:1397-1419), which stalls the whole CTA on
 // one query at a time.
-// Kernel variant (template MODE) of the strip sampler whose warps also share very long rows: kept
-// apart because the sharing code costs the plain sweep registers (48 against 40, one CTA per SM less)
-// and about 20 % of its throughput; the engine selects it for graphs that have rows long enough to
-// leave a tail.
-constexpr int kModeStripShared = FW_GROUP_STRIP + 1;
 constexpr uint32_t kCoopMinSupers = 16;   // rows from 16 supergroups (about 32,000 edges) may be shared
 constexpr uint32_t kCoopChunkSupers = 4;  // supergroups per ticket (32 KB)
 constexpr uint32_t kCoopSpinLimit = 1u << 22;
@@ -957,7 +962,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
   if (ringed && lane == 0) {
 #pragma unroll
     for (uint32_t t = 0; t < kStages; ++t)
-      if (1u + t < last_b) ring_fill<SweepApp<APP>::value>(c, ring, 1u + t, t);
+      if (1u + t < last_b) ring_fill<SweepApp<APP, MODE>::value>(c, ring, 1u + t, t);
   }
   SuperAcc acc{0.0f, 0.0f, 0u, 0u, r};
   // A very long row is posted for the CTA's idle warps, which take supergroups from the back.
@@ -972,13 +977,13 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     if (lane == 0) k = ld_volatile(&task->ticket) & 0xFFFFu;
     return (b >> 2) + __shfl_sync(0xFFFFFFFFu, k, 0) * kCoopChunkSupers >= end_super;
   };
-  absorb<APP, CLEAN>(a, c, acc, best, sub_first<SweepApp<APP>::value, CLEAN>(a, c, nb > 1u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
+  absorb<APP, CLEAN>(a, c, acc, best, sub_first<SweepApp<APP, MODE>::value, CLEAN>(a, c, nb > 1u, lane), 0u, nb == 1u, false, lane, c1, qlo, qhi);
   uint32_t b = 1;
   if (!ringed) {
 #pragma unroll 1
     for (; b < last_b; ++b) {
       if (posted && (b & 3u) == 0u && taken(b)) break;
-      absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, b, lane), b, false, true, lane, c1, qlo, qhi);
+      absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP, MODE>::value, CLEAN>(a, c, b, lane), b, false, true, lane, c1, qlo, qhi);
     }
   } else {
     uint32_t t = 0;
@@ -998,7 +1003,7 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
         break;
       }
       float A;
-      if (!ring_sub<SweepApp<APP>::value, CLEAN>(a, c, b, last_b, lane, ring, ring_ptr, t, A)) {
+      if (!ring_sub<SweepApp<APP, MODE>::value, CLEAN>(a, c, b, last_b, lane, ring, ring_ptr, t, A)) {
         ring.failed = true;
         return 0xFFFFFFFFu;
       }
@@ -1016,10 +1021,10 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
       acc.r = fw::philox4x32_10(acc.g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
 #pragma unroll 1
       for (b = 4u * end_super; b < last_b; ++b)
-        absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, b, lane), b, false, false, lane, c1, qlo, qhi);
+        absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP, MODE>::value, CLEAN>(a, c, b, lane), b, false, false, lane, c1, qlo, qhi);
     }
   }
-  if (nb > 1u) absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP>::value, CLEAN>(a, c, last_b, lane), last_b, true, false, lane, c1, qlo, qhi);
+  if (nb > 1u) absorb<APP, CLEAN>(a, c, acc, best, sub_global<SweepApp<APP, MODE>::value, CLEAN>(a, c, last_b, lane), last_b, true, false, lane, c1, qlo, qhi);
   warp_argmin(best.key, best.id);
   uint32_t B = best.id;
   if (posted) {
@@ -1030,13 +1035,13 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     if (B != 0xFFFFFFFFu && fin != own) {  // another warp reduced the winning strip
       const unsigned long long pw = strip_redo<APP, CLEAN>(a, c, B, c1, qlo, qhi, lane);
       if (APP == FW_APP_NODE2VEC && c.prev >= 0) return n2v_pick<CLEAN>(a, c, B, (uint32_t)(pw >> 32), lane);
-      return pick_in_row<SweepApp<APP>::value, CLEAN>(a, c, B, (uint32_t)(pw >> 32), __uint_as_float((uint32_t)pw), lane);
+      return pick_in_row<SweepApp<APP, MODE>::value, CLEAN>(a, c, B, (uint32_t)(pw >> 32), __uint_as_float((uint32_t)pw), lane);
     }
   }
   if (B == 0xFFFFFFFFu) return B;
   if (APP == FW_APP_NODE2VEC && c.prev >= 0)
     return n2v_pick<CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)), lane);
-  return pick_in_row<SweepApp<APP>::value, CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)),
+  return pick_in_row<SweepApp<APP, MODE>::value, CLEAN>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u)),
                                                   __shfl_sync(0xFFFFFFFFu, best.W, (int)(B & 31u)), lane);
 }
 
@@ -1055,7 +1060,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE ? kStages * stage_bytes<SweepApp<APP>::value>() : 0u;
+  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE ? kStages * stage_bytes<SweepApp<APP, MODE>::value>() : 0u;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
   Ring ring;
