@@ -1,7 +1,8 @@
 #!/bin/bash
 # Builds the reference's CUDA walker for sm_100 from its own sources where they lie
-# (/root/reference, read-only) plus the harness and the gflags stand-in of this folder.
-# Output only into oracle/_ref/ (git-ignored, travels to the GPU box).  Flags follow the
+# (the read-only checkout named by FW_REFERENCE_DIR, see the default below) plus the harness
+# and the gflags stand-in of this folder.
+# Output only into oracle/_ref/ (kept out of git; it ships with the tree like the built library).  Flags follow the
 # reference's CMakeLists.txt:28-49 (-O3 -lineinfo -maxrregcount=32, relocatable device code).
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
