@@ -33,11 +33,13 @@ def main():
     ap.add_argument("--degrees", default="16,128,1024,8192,65536")
     ap.add_argument("--d", type=int, default=40)
     ap.add_argument("--group", type=int, default=0)
+    ap.add_argument("--work", type=float, default=0.0,
+                    help="neighbours to scan per launch (default 4e11; a small value keeps instrumented ncu captures short)")
     args = ap.parse_args()
     for degree in [int(x) for x in args.degrees.split(",")]:
         g, V = regular_graph(degree)
         eng = fw.Engine(g, 0)
-        target = 4e11 if degree >= 64 else 5e10
+        target = args.work or (4e11 if degree >= 64 else 5e10)
         n = int(min(max(target / (degree * args.d), 20000), 8e6))
         starts = torch.from_numpy(np.random.default_rng(2).integers(0, V, n).astype(np.int32)).cuda()
         res = torch.empty((n, args.d + 1), dtype=torch.int32, device="cuda")
