@@ -6,5 +6,5 @@ engine, and loading fails loudly when the library has not been built.
 """
 from ._binding import (  # noqa: F401
     APP_DEEPWALK, APP_METAPATH, APP_NODE2VEC, APP_PPR, ENGINE_MANAGED, GROUP_EDGE, GROUP_STRIP,
-    Engine, FlowWalkerError, Graph, WalkStats, lib, lib_path, make_params, rmat,
+    Engine, FlowWalkerError, Graph, WalkStats, lib, lib_path, lognormal_weights, make_params, rmat,
 )

@@ -64,6 +64,7 @@ def lib():
         L.fw_graph_from_edgelist.argtypes = [ctypes.c_char_p, i32, ctypes.c_float, ctypes.c_float,
                                              ctypes.c_uint64, ctypes.POINTER(vp)]
         L.fw_rmat_generate.argtypes = [ctypes.POINTER(_Rmat), ctypes.POINTER(vp)]
+        L.fw_lognormal_weights.argtypes = [i64, ctypes.c_double, ctypes.c_double, ctypes.c_uint64, vp]
         L.fw_graph_info.argtypes = [vp, ctypes.POINTER(i64), ctypes.POINTER(i64), ctypes.POINTER(i32),
                                     ctypes.POINTER(i32), ctypes.POINTER(i32)]
         L.fw_graph_arrays.argtypes = [vp] + [ctypes.POINTER(vp)] * 4
@@ -84,6 +85,10 @@ def lib():
                                          ctypes.POINTER(WalkStats), vp]
         L.fw_free_pinned.argtypes = [vp]
         L.fw_free_pinned.restype = None
+        L.fw_selftest_wait_timeout.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint32)]
+        L.fw_walk_csr_noalloc.argtypes = [ctypes.c_int, i64, i64, vp, ctypes.c_int, vp, vp, vp,
+                                          ctypes.POINTER(_Params), vp, i64, vp, vp,
+                                          ctypes.POINTER(WalkStats), vp]
         _lib = L
     return _lib
 
@@ -257,3 +262,10 @@ class Engine:
             self.close()
         except Exception:
             pass
+
+
+def lognormal_weights(n, mean=0.0, sigma=3.0, seed=1234):
+    """Seeded log-normal weights (fw_lognormal_weights): what the CLI's --lognorm puts on the edges."""
+    out = np.empty(n, dtype=np.float32)
+    _check(lib().fw_lognormal_weights(n, mean, sigma, seed, out.ctypes.data))
+    return out

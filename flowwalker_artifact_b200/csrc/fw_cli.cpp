@@ -55,6 +55,7 @@ void define_flags(fwflags::Parser& fl) {
   fl.add("uniformstarts", Flag::kBool, "false", "ppr: seeded uniform start points instead of the max-degree vertex");
   fl.add("group", Flag::kInt, "0", "sampler granularity: 0 default, 1 per neighbour, 64 per strip");
   fl.add("gpus", Flag::kInt, "1", "number of GPUs: queries are sharded, the graph is replicated");
+  fl.add("shards", Flag::kInt, "0", "query shards (0 = one per GPU); shard r walks ids [r*n/S, (r+1)*n/S) on GPU r mod --gpus with a replica of its own");
   fl.add("save_result", Flag::kString, "", "write the int32 [n x (d+1)] walk table to this file");
   fl.add("edgelist", Flag::kString, "", "build the graph from this text edge list instead of reading --input");
   fl.add("save_csr", Flag::kString, "", "write the graph as <prefix>_xadj/_edge/_weight/_label.bin and exit");
@@ -192,9 +193,7 @@ int main(int argc, char** argv) {
          (long long)gv.E, (long long)maxd, (long long)maxv);
   if (fl.b("lognorm") && !metapath) {  // include/graph.cuh:79-91 (seed 1234, mean 0, sigma 3)
     std::vector<float> w((size_t)gv.E);
-    std::mt19937_64 rng(1234);
-    std::lognormal_distribution<float> dist(0.0f, 3.0f);
-    for (auto& x : w) x = dist(rng);
+    if (fw_lognormal_weights(gv.E, 0.0, 3.0, 1234, w.data()) != FW_OK) return fail("lognorm");
     fw_graph* g2 = nullptr;
     if (fw_graph_from_arrays(gv.V, gv.E, gv.xadj, gv.bits, gv.adj, w.data(), nullptr, &g2) != FW_OK) return fail("lognorm");
     fw_graph_destroy(g);
@@ -244,19 +243,22 @@ int main(int argc, char** argv) {
   if (fw_device_count(&visible) != FW_OK) return fail("device count");
   if (gpus < 1 || gpus > visible) { fprintf(stderr, "flowwalker: --gpus %d but %d device(s) visible\n", gpus, visible); return 2; }
 
-  // one engine per GPU, queries sharded by contiguous id range, graph replicated
+  // one engine per shard (by default one shard per GPU), queries sharded by contiguous id
+  // range, graph replicated; the walks are keyed by query id, so any sharding gives the same table
+  const int shards = fl.i("shards") > 0 ? (int)fl.i("shards") : gpus;
+  if (shards > 64) { fprintf(stderr, "flowwalker: --shards %d is beyond 64\n", shards); return 2; }
   std::vector<int32_t> result((size_t)n * depth);
-  std::vector<fw_walk_stats> stats((size_t)gpus);
-  std::vector<int> rcs((size_t)gpus, FW_OK);
-  std::vector<std::string> errs((size_t)gpus);
-  std::vector<fw_engine*> engines((size_t)gpus, nullptr);
-  for (int r = 0; r < gpus; ++r)
-    if (fw_engine_create(g, r, fl.b("umgraph") ? FW_ENGINE_MANAGED : 0, &engines[(size_t)r]) != FW_OK) return fail("engine");
+  std::vector<fw_walk_stats> stats((size_t)shards);
+  std::vector<int> rcs((size_t)shards, FW_OK);
+  std::vector<std::string> errs((size_t)shards);
+  std::vector<fw_engine*> engines((size_t)shards, nullptr);
+  for (int r = 0; r < shards; ++r)
+    if (fw_engine_create(g, r % gpus, fl.b("umgraph") ? FW_ENGINE_MANAGED : 0, &engines[(size_t)r]) != FW_OK) return fail("engine");
   const auto t0 = std::chrono::steady_clock::now();
   std::vector<std::thread> threads;
-  for (int r = 0; r < gpus; ++r) {
+  for (int r = 0; r < shards; ++r) {
     threads.emplace_back([&, r]() {
-      const int64_t lo = r * n / gpus, hi = (r + 1) * n / gpus;
+      const int64_t lo = r * n / shards, hi = (r + 1) * n / shards;
       fw_walk_params p = prm;
       p.query_id_base = (uint64_t)lo;
       int rc;
@@ -276,8 +278,8 @@ int main(int argc, char** argv) {
   }
   for (auto& t : threads) t.join();
   const double wall_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-  for (int r = 0; r < gpus; ++r) {
-    if (rcs[(size_t)r] != FW_OK) { fprintf(stderr, "flowwalker: walk on GPU %d: %s\n", r, errs[(size_t)r].c_str()); return 1; }
+  for (int r = 0; r < shards; ++r) {
+    if (rcs[(size_t)r] != FW_OK) { fprintf(stderr, "flowwalker: walk of shard %d on GPU %d: %s\n", r, r % gpus, errs[(size_t)r].c_str()); return 1; }
   }
   uint64_t steps = 0, scanned = 0;
   double dev_ms = 0;

@@ -11,6 +11,7 @@
 // 0xFFFFFFFF when it does not fit) followed by int64 xadj[V+1]; told apart by
 // the file size.
 #include <errno.h>
+#include <math.h>
 #include <stdio.h>
 #include <string.h>
 #include <sys/stat.h>
@@ -327,5 +328,24 @@ extern "C" int fw_graph_from_edgelist(const char* path, int32_t n_labels, float 
     if (labels) g->label[e] = (int32_t)(((uint64_t)r.y * (uint32_t)n_labels) >> 32);
   }
   *out = g;
+  return FW_OK;
+}
+
+// --lognorm (include/graph.cuh:79-91).  One Philox block per pair of values: words 0,1 -> u1 in
+// (0,1), words 2,3 -> u2 in [0,1), each with 53 bits; Box-Muller gives z = r cos(t), r sin(t).
+extern "C" int fw_lognormal_weights(int64_t n, double mean, double sigma, uint64_t seed, float* out) {
+  fw::clear_error();
+  if (n < 0 || (n > 0 && !out)) return fw::fail(FW_ERR_ARG, "fw_lognormal_weights: bad arguments");
+  const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  const double two_pi = 6.283185307179586476925286766559;
+  for (int64_t i = 0; i < n; i += 2) {
+    const uint64_t blk = (uint64_t)i >> 1;
+    const fw::Philox4 r = fw::philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), 0x4C4F474Eu, 0u, k0, k1);
+    const uint64_t a = (((uint64_t)r.x << 32) | r.y) >> 11, b = (((uint64_t)r.z << 32) | r.w) >> 11;
+    const double u1 = ((double)a + 0.5) * 0x1p-53, u2 = (double)b * 0x1p-53;
+    const double rad = sqrt(-2.0 * log(u1)), ang = two_pi * u2;
+    out[i] = (float)exp(mean + sigma * rad * cos(ang));
+    if (i + 1 < n) out[i + 1] = (float)exp(mean + sigma * rad * sin(ang));
+  }
   return FW_OK;
 }

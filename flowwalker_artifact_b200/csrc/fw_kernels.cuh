@@ -753,14 +753,28 @@ __device__ __forceinline__ bool sweep_supers(const WalkArgs& a, const StepCtx& c
   return true;
 }
 
+// The out-of-line helpers below receive the kernel arguments by address.  They read the fields
+// of a row sweep once into a local copy: every field that sweep_supers, sub_global, absorb,
+// n2v_test, n2v_strip_exact or the Philox calls read must be listed here (the rest of the copy is
+// never read and costs nothing).
+__device__ __forceinline__ WalkArgs sweep_args(const WalkArgs& args) {
+  WalkArgs a;
+  a.adj = args.adj;
+  a.inv_p = args.inv_p;
+  a.inv_q = args.inv_q;
+  a.n2v_fmax = args.n2v_fmax;  // bound of node2vec's optimistic key (n2v_test)
+  a.k0 = args.k0;
+  a.k1 = args.k1;
+  return a;
+}
+
 // An idle warp serves tickets of the posted row until they stop being valid.  Every lane of the
 // warp must call it.  Returns the warp's ring parity in bits 1.., and in bit 0 whether all went
 // well (0: a staged copy did not arrive).  Out of line: only idle warps run it.
 template <int APP, bool CLEAN>
 __device__ __noinline__ uint32_t coop_serve(const WalkArgs& args, CoopTask* task, uint32_t lane, Ring ring,
                                             const unsigned char* ring_ptr, uint32_t* my_flags) {
-  WalkArgs a;  // the kernel arguments arrive by address here: read the few fields the sweep needs once
-  a.adj = args.adj; a.inv_p = args.inv_p; a.inv_q = args.inv_q; a.k0 = args.k0; a.k1 = args.k1;
+  const WalkArgs a = sweep_args(args);
   for (;;) {
     unsigned int tk = 0, mine = 0;
     if (lane == 0) {
@@ -870,8 +884,7 @@ __device__ __noinline__ unsigned long long coop_close(CoopTask* task, uint32_t t
 template <int APP, bool CLEAN>
 __device__ __noinline__ unsigned long long strip_redo(const WalkArgs& args, StepCtx c, uint32_t B, uint32_t c1,
                                                       uint32_t qlo, uint32_t qhi, uint32_t lane) {
-  WalkArgs a;
-  a.adj = args.adj; a.inv_p = args.inv_p; a.inv_q = args.inv_q; a.k0 = args.k0; a.k1 = args.k1;
+  const WalkArgs a = sweep_args(args);
   const uint32_t sW = B >> 5, lW = B & 31u;
   const uint32_t last_b = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub - 1u;
   const uint32_t pick = fw::philox4x32_10((sW / 3u) * 32u + lW, c1, qlo, qhi, a.k0, a.k1).w;

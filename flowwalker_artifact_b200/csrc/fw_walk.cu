@@ -70,7 +70,12 @@ namespace {
 
 struct DeviceGuard {
   int prev = 0;
-  explicit DeviceGuard(int dev) { cudaGetDevice(&prev); cudaSetDevice(dev); }
+  bool ok = false;  // the requested device is current
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    int now = -1;
+    ok = cudaSetDevice(dev) == cudaSuccess && cudaGetDevice(&now) == cudaSuccess && now == dev;
+  }
   ~DeviceGuard() { cudaSetDevice(prev); }
 };
 
@@ -133,6 +138,21 @@ int check_params(const fw_engine* e, const fw_walk_params* p, int64_t n) {
   return FW_OK;
 }
 
+// Lets `fn` use `smem` bytes of dynamic shared memory and returns how many of its CTAs fit on an
+// SM.  Without the opt-in a kernel's dynamic and static shared memory together are limited to
+// 48 KB, so the test counts the kernel's static part as well (the walk kernels hold their
+// mbarriers, node2vec's match flags and the CTA's board there).
+int prepare_kernel(KernelFn fn, size_t smem, int* per_sm) {
+  cudaFuncAttributes attr;
+  FW_CUDA(cudaFuncGetAttributes(&attr, (const void*)fn));
+  if (smem + attr.sharedSizeBytes > 48 * 1024)
+    FW_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  *per_sm = 0;
+  FW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, fn, kThreads, smem));
+  if (*per_sm < 1) return fw::fail(FW_ERR_CUDA, "walk kernel does not fit on an SM");
+  return FW_OK;
+}
+
 // Enqueues: scratch reset, kernel between ev[0] and ev[1], scratch read-back.
 int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_dev, int64_t n,
                  int32_t* result_dev, cudaStream_t st, cudaEvent_t ev_begin, cudaEvent_t ev_end,
@@ -156,11 +176,9 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
                       (e->sharing < 0 && p->app != FW_APP_NODE2VEC && e->max_degree >= kSharingAutoDegree);
   KernelFn fn = pick_kernel(p->app, mode, e->clean_weights, shared, e->xadj_bits);
   const size_t smem = kernel_smem_bytes(p->app, mode, p->d, a.hist_in_smem != 0);
-  if (smem > 48 * 1024)
-    FW_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
-  FW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
-  if (per_sm < 1) return fw::fail(FW_ERR_CUDA, "walk kernel does not fit on an SM");
+  const int prc = prepare_kernel(fn, smem, &per_sm);
+  if (prc) return prc;
   const size_t words = (size_t)kSlotHist + (size_t)p->d + 1;
   FW_CUDA(cudaMemsetAsync(d_scratch, 0, words * 8, st));
   FW_CUDA(cudaEventRecord(ev_begin, st));
@@ -479,6 +497,7 @@ extern "C" int fw_selftest_wait_timeout(int device, uint32_t polls, uint32_t* st
   if (!status) return fw::fail(FW_ERR_ARG, "fw_selftest_wait_timeout: null argument");
   if (polls == 0 || polls > (1u << 20)) return fw::fail(FW_ERR_ARG, "polls must be in 1..2^20");
   DeviceGuard guard(device);
+  if (!guard.ok) return fw::fail(FW_ERR_ARG, "device %d cannot be made current", device);
   unsigned int* d = nullptr;
   FW_CUDA(cudaMalloc(&d, sizeof(unsigned int)));
   cudaError_t err = cudaMemset(d, 0, sizeof(unsigned int));
@@ -524,6 +543,9 @@ int noalloc_scratch_for(int device, unsigned long long** out) {
   static std::mutex table_mu;
   std::lock_guard<std::mutex> lock(table_mu);
   if (!g_noalloc_ptr[device]) {
+    int now = -1;
+    if (cudaGetDevice(&now) != cudaSuccess || now != device)
+      return fw::fail(FW_ERR_CUDA, "device %d is not current; the scratch address cannot be looked up", device);
     void* p = nullptr;
     cudaError_t err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (err != cudaSuccess || !p)
@@ -562,7 +584,13 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
   if (n > 0 && (!starts_dev || !result_dev)) return fw::fail(FW_ERR_ARG, "null device buffer");
   if (((uintptr_t)adj_dev | (uintptr_t)weight_dev | (uintptr_t)label_dev) & 15u)
     return fw::fail(FW_ERR_ARG, "edge arrays must be 16-byte aligned");
+  int count = 0, cc_major = 0;
+  FW_CUDA(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count) return fw::fail(FW_ERR_ARG, "device %d out of range (%d visible)", device, count);
+  FW_CUDA(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
+  if (cc_major < 10) return fw::fail(FW_ERR_CUDA, "device %d is below sm_100; this library is built for sm_100a only", device);
   DeviceGuard guard(device);
+  if (!guard.ok) return fw::fail(FW_ERR_CUDA, "cudaSetDevice(%d) failed", device);
   unsigned long long* scratch = nullptr;
   int rc = noalloc_scratch_for(device, &scratch);
   if (rc) return rc;
@@ -584,12 +612,10 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
   const int mode = p->group_mode == 0 ? FW_GROUP_STRIP : p->group_mode;
   KernelFn fn = pick_kernel(p->app, mode, /*clean=*/false, /*shared=*/false, xadj_bits);  // caller's arrays: not inspected
   const size_t smem = kernel_smem_bytes(p->app, mode, p->d, true);
-  if (smem > 48 * 1024)
-    FW_CUDA(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0, sms = 0;
-  FW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem));
+  rc = prepare_kernel(fn, smem, &per_sm);
+  if (rc) return rc;
   FW_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  if (per_sm < 1) return fw::fail(FW_ERR_CUDA, "walk kernel does not fit on an SM");
   const size_t words = (size_t)kSlotHist + (size_t)p->d + 1;
   // the array keeps the previous call's counters: everything this call reads starts at zero
   FW_CUDA(cudaMemsetAsync(scratch, 0, words * 8, st));

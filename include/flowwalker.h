@@ -115,6 +115,11 @@ int fw_rmat_generate(const fw_rmat_params* params, fw_graph** out);
  * converter does (data/EdgeListToCSR.cpp:132-268); rows sorted, self-loops dropped, attributes seeded. */
 int fw_graph_from_edgelist(const char* path, int32_t n_labels, float weight_lo, float weight_hi,
                            uint64_t seed, fw_graph** out);
+/* Seeded log-normal edge weights, the job of --lognorm (include/graph.cuh:79-91: mean 0, sigma 3,
+ * seed 1234 there, drawn with cuRAND).  out[i] = exp(mean + sigma * z_i), z_i a standard normal
+ * formed by the Box-Muller transform from Philox4x32-10 block i / 2 keyed by `seed`; computed in
+ * double precision and rounded to float, so the values depend on the seed only. */
+int fw_lognormal_weights(int64_t n, double mean, double sigma, uint64_t seed, float* out);
 int fw_graph_info(const fw_graph* g, int64_t* V, int64_t* E, int32_t* xadj_bits,
                   int32_t* has_weight, int32_t* has_label);
 /* Borrowed pointers into the graph (valid until fw_graph_destroy). */
@@ -206,18 +211,27 @@ int fw_selftest_wait_timeout(int device, uint32_t polls, uint32_t* status);
  *
  * Limits and rules:
  *  - d <= 4095 (larger values are rejected with FW_ERR_ARG: use fw_walk_device);
- *    device ordinal < 64; schema_len <= 64.
- *  - adj_dev / weight_dev / label_dev must be 16-byte aligned and readable up
+ *    device ordinal < 64 and visible, compute capability >= 10; schema_len <= 64.
+ *  - xadj_dev holds V + 1 row offsets (32- or 64-bit as xadj_bits says).
+ *    adj_dev / weight_dev / label_dev must be 16-byte aligned and readable up
  *    to the next multiple of 4 elements past E (the kernel reads whole
  *    16-byte quads); weight_dev may be NULL for MetaPath, label_dev otherwise.
- *  - The first call on each device looks up the scratch address
- *    (cudaGetSymbolAddress); make that first call before any stream capture.
+ *    node2vec needs every row of adj_dev sorted ascending (its membership test
+ *    is a binary search, as include/gpu_graph.cuh:97-118).
+ *  - `stream` is a cudaStream_t; NULL here is the legacy default stream (not an
+ *    engine's own stream as in fw_walk_device: there is no engine).
+ *  - The first call on each device is a set-up call: it looks up the scratch
+ *    address (cudaGetSymbolAddress) and, with lazy module loading, may make
+ *    the driver load the kernel (which allocates inside the driver).  Make
+ *    that first call at start-up, outside any stream capture.  The promise
+ *    "no allocating call" holds for every call after it.
  *  - All calls on one device share the scratch array, which keeps the last
  *    call's contents; each call clears what it uses, so calls must not overlap
  *    on the GPU (two streams, or two host threads on the same device, race).
- *  - Returns after the kernel has finished; stats->device_ms / total_ms are
- *    not measured (0) since events would have to be created.  len_hist
- *    (optional, host, d+1 words) receives the walk-length counts.
+ *  - The call synchronises `stream` and returns after the kernel has finished
+ *    (counters travel back by plain copies); stats->device_ms / total_ms are
+ *    not measured (0) since events would have to be created.  stats and
+ *    len_hist (host, d+1 words) may be NULL.
  */
 int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void* xadj_dev, int xadj_bits,
                         const int32_t* adj_dev, const float* weight_dev, const int32_t* label_dev,

@@ -114,10 +114,14 @@ def test_from_arrays_validation():
     assert g.xadj_bits == 64 and g.max_degree() == (0, 1)
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/data/wiki-Vote_xadj.bin"),
-                    reason="the reference's bundled sample graph is not mounted")
+# the reference checkout, when one is at hand (FW_REFERENCE_DIR, as oracle/build_ref.sh reads it)
+REFERENCE_SAMPLE = os.path.join(os.environ.get("FW_REFERENCE_DIR", ""), "data", "wiki-Vote")
+
+
+@pytest.mark.skipif(not os.path.exists(REFERENCE_SAMPLE + "_xadj.bin"),
+                    reason="FW_REFERENCE_DIR does not point at a reference checkout with its sample graph")
 def test_reads_the_reference_sample_graph():
-    g = fw.Graph.load("/root/reference/data/wiki-Vote", True, True)
+    g = fw.Graph.load(REFERENCE_SAMPLE, True, True)
     assert (g.V, g.E) == (7115, 201524)
     assert g.max_degree()[1] == 1065
     assert g.weight.min() > 0 and g.weight.max() < 5 and set(np.unique(g.label)) == {0, 1, 2, 3, 4}

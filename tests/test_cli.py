@@ -25,7 +25,8 @@ def test_flag_errors_and_help():
     assert r.returncode == 0
     for flag in ("--input", "--n", "--all", "--d", "--deepwalk", "--ppr", "--node2vec", "--metapath", "--tp",
                  "--p", "--q", "--schema", "--batchsize", "--autobatch", "--headroom", "--printresult",
-                 "--printworkload", "--save_degree", "--b_file", "--walkmode", "--dprs", "--syn", "--lognorm"):
+                 "--printworkload", "--save_degree", "--b_file", "--walkmode", "--dprs", "--syn", "--lognorm",
+                 "--shards"):
         assert flag + " " in r.stdout, flag
     assert run("--bogus").returncode == 2
     assert run("--n", "abc").returncode == 2
@@ -115,9 +116,47 @@ def test_cli_two_gpus_and_int64_offsets(tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     ref = O.graph_walk(g, fw.APP_DEEPWALK, np.arange(g.V, dtype=np.int32), d=12)[0]
     assert (np.fromfile(out1, dtype=np.int32).reshape(g.V, 13) == ref).all()
+    # three shards on one device: the sharded path (id ranges, id bases, one engine and one host
+    # thread per shard, results merged) with whatever number of devices is visible
+    out3 = str(tmp_path / "w3.bin")
+    r = run("--input", prefix, "--deepwalk", "--all", "--d", "12", "--shards", "3", "--save_result", out3)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert (np.fromfile(out3, dtype=np.int32).reshape(g.V, 13) == ref).all()
     if n_dev.value < 2:
         pytest.skip("one visible device: the two-device half of this test needs two")
     out2 = str(tmp_path / "w2.bin")
     r = run("--input", prefix, "--deepwalk", "--all", "--d", "12", "--gpus", "2", "--save_result", out2)
     assert r.returncode == 0, r.stdout + r.stderr
     assert (np.fromfile(out2, dtype=np.int32).reshape(g.V, 13) == ref).all()
+
+
+def test_lognormal_weights_are_seeded_and_log_normal():
+    """--lognorm's weights (include/graph.cuh:79-91: log-normal, mean 0, sigma 3): a function of the
+    seed alone (Philox + Box-Muller, no library distribution object), with the moments asked for."""
+    w = fw.lognormal_weights(200001)
+    assert w.dtype == np.float32 and (w > 0).all() and np.isfinite(w).all()
+    assert [float(x).hex() for x in w[:4]] == ["0x1.3fc2700000000p-2", "0x1.7bd8440000000p-3",
+                                               "0x1.8436b20000000p+7", "0x1.4381020000000p+3"]
+    assert (fw.lognormal_weights(1001) == w[:1001]).all()          # a prefix, whatever the count
+    assert (fw.lognormal_weights(1000, seed=5) != w[:1000]).any()
+    lg = np.log(w.astype(np.float64))
+    assert abs(lg.mean()) < 0.03 and abs(lg.std() - 3.0) < 0.03
+    z = lg / 3.0                                                     # standard normal: check a few quantiles
+    for qq, zq in ((0.1, -1.2816), (0.5, 0.0), (0.9, 1.2816), (0.99, 2.3263)):
+        assert abs(np.quantile(z, qq) - zq) < 0.03
+    small = fw.lognormal_weights(5, mean=1.0, sigma=0.0)
+    assert np.allclose(small, np.e, rtol=1e-6)
+
+
+@pytest.mark.gpu
+def test_cli_lognorm_walks_use_those_weights(tmp_path):
+    g = graphs.config1()
+    prefix = str(tmp_path / "g")
+    g.save(prefix)
+    out = str(tmp_path / "walks.bin")
+    r = run("--input", prefix, "--deepwalk", "--all", "--d", "15", "--lognorm", "--save_result", out)
+    assert r.returncode == 0, r.stdout + r.stderr
+    walks = np.fromfile(out, dtype=np.int32).reshape(g.V, 16)
+    ref = O.walk(g.xadj, g.adj, fw.lognormal_weights(g.E), None, fw.APP_DEEPWALK,
+                 np.arange(g.V, dtype=np.int32), d=15)[0]
+    assert (walks == ref).all()

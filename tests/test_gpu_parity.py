@@ -69,8 +69,20 @@ def test_star_hub(app, kw, mode):
     assert_same(run_both(arrs, app, kw, starts, mode))
 
 
+@pytest.mark.parametrize("app,d", [(fw.APP_DEEPWALK, 4095), (fw.APP_DEEPWALK, 4000), (fw.APP_NODE2VEC, 3800),
+                                   (fw.APP_NODE2VEC, 4095), (fw.APP_PPR, 4096), (fw.APP_DEEPWALK, 9000)])
+def test_long_walks_around_the_shared_memory_limits(app, d):
+    """Walk lengths at which the length histogram plus the staging rings reach 48 KB of shared
+    memory (the kernel's static part counts too) and at which the histogram leaves shared memory."""
+    g = graphs.config1()
+    arrs = dict(xadj=g.xadj.copy(), adj=g.adj.copy(), weight=g.weight.copy(), label=g.label.copy())
+    kw = dict(d=d, tp=0.001) if app == fw.APP_PPR else dict(d=d)
+    assert_same(run_both(arrs, app, kw, graphs.config1_starts(96, seed=d), fw.GROUP_STRIP))
+
+
 @pytest.mark.parametrize("n", [3, 9, 64, 1000])
-@pytest.mark.parametrize("app,kw", APPS)
+@pytest.mark.parametrize("app,kw", APPS + [(fw.APP_NODE2VEC, dict(d=80, p=0.25, q=4.0)),
+                                          (fw.APP_NODE2VEC, dict(d=80, p=4.0, q=0.25))])
 def test_star_hub_shared_between_warps(app, kw, n):
     """Rows of 100,000 edges with the block-granularity path forced on: warps that are out of
     queries take supergroups from the back of a posted row; the walks must not change.  With 3 or
@@ -139,7 +151,6 @@ def test_bounded_wait_reports_instead_of_hanging():
     leaves the context usable (the next walk still matches the golden walker)."""
     import ctypes
     L = fw.lib()
-    L.fw_selftest_wait_timeout.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint32)]
     status = ctypes.c_uint32(0)
     assert L.fw_selftest_wait_timeout(0, 2000, ctypes.byref(status)) == 0, L.fw_last_error()
     assert status.value == 4  # FW_STATUS_WAIT_TIMEOUT
