@@ -21,7 +21,7 @@ class _Params(ctypes.Structure):
                 ("p", ctypes.c_double), ("q", ctypes.c_double),
                 ("schema", ctypes.POINTER(ctypes.c_int32)), ("schema_len", ctypes.c_int32),
                 ("group_mode", ctypes.c_int32), ("seed", ctypes.c_uint64),
-                ("query_id_base", ctypes.c_uint64)]
+                ("query_id_base", ctypes.c_uint64), ("query_id_stride", ctypes.c_uint64)]
 
 
 class WalkStats(ctypes.Structure):
@@ -56,6 +56,7 @@ def lib():
             raise FlowWalkerError(-100, "%s is missing: run `python -m flowwalker_artifact_b200.build`" % path)
         L = ctypes.CDLL(path)
         L.fw_last_error.restype = ctypes.c_char_p
+        L.fw_kernel_revision.restype = ctypes.c_char_p
         vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32
         L.fw_device_count.argtypes = [ctypes.POINTER(ctypes.c_int)]
         L.fw_graph_load.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(vp)]
@@ -98,7 +99,8 @@ def _check(rc):
         raise FlowWalkerError(rc, lib().fw_last_error().decode("utf-8", "replace"))
 
 
-def make_params(app, d=80, tp=0.2, p=2.0, q=0.5, schema=None, group_mode=0, seed=1337, query_id_base=0):
+def make_params(app, d=80, tp=0.2, p=2.0, q=0.5, schema=None, group_mode=0, seed=1337, query_id_base=0,
+                query_id_stride=1):
     """Returns (struct, keepalive) for a fw_walk_params."""
     prm = _Params()
     prm.app, prm.d, prm.tp, prm.p, prm.q = app, d, tp, p, q
@@ -108,6 +110,7 @@ def make_params(app, d=80, tp=0.2, p=2.0, q=0.5, schema=None, group_mode=0, seed
         prm.schema = keep.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))
         prm.schema_len = len(keep)
     prm.group_mode, prm.seed, prm.query_id_base = group_mode, seed, query_id_base
+    prm.query_id_stride = query_id_stride
     return prm, keep
 
 

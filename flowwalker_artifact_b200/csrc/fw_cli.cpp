@@ -56,6 +56,7 @@ void define_flags(fwflags::Parser& fl) {
   fl.add("group", Flag::kInt, "0", "sampler granularity: 0 default, 1 per neighbour, 64 per strip");
   fl.add("gpus", Flag::kInt, "1", "number of GPUs: queries are sharded, the graph is replicated");
   fl.add("shards", Flag::kInt, "0", "query shards (0 = one per GPU); shard r walks ids [r*n/S, (r+1)*n/S) on GPU r mod --gpus with a replica of its own");
+  fl.add("interleave", Flag::kBool, "false", "shard r of S walks the ids r, r+S, r+2S, ... instead of a contiguous id range");
   fl.add("save_result", Flag::kString, "", "write the int32 [n x (d+1)] walk table to this file");
   fl.add("edgelist", Flag::kString, "", "build the graph from this text edge list instead of reading --input");
   fl.add("save_csr", Flag::kString, "", "write the graph as <prefix>_xadj/_edge/_weight/_label.bin and exit");
@@ -258,6 +259,22 @@ int main(int argc, char** argv) {
   std::vector<std::thread> threads;
   for (int r = 0; r < shards; ++r) {
     threads.emplace_back([&, r]() {
+      if (fl.b("interleave") && shards > 1) {
+        // ids r, r + S, ...: gather the shard's start points, walk, scatter its rows back
+        const int64_t m = n > r ? (n - r + shards - 1) / shards : 0;
+        std::vector<int32_t> st((size_t)m), res((size_t)m * depth);
+        for (int64_t i = 0; i < m; ++i) st[(size_t)i] = starts[(size_t)(r + i * shards)];
+        fw_walk_params p = prm;
+        p.query_id_base = (uint64_t)r;
+        p.query_id_stride = (uint64_t)shards;
+        const int rc = fw_walk(engines[(size_t)r], &p, st.data(), m, res.data(), &stats[(size_t)r], nullptr);
+        if (rc == FW_OK)
+          for (int64_t i = 0; i < m; ++i)
+            memcpy(result.data() + (size_t)(r + i * shards) * depth, res.data() + (size_t)i * depth, (size_t)depth * 4);
+        rcs[(size_t)r] = rc;
+        if (rc != FW_OK) errs[(size_t)r] = fw_last_error();
+        return;
+      }
       const int64_t lo = r * n / shards, hi = (r + 1) * n / shards;
       fw_walk_params p = prm;
       p.query_id_base = (uint64_t)lo;

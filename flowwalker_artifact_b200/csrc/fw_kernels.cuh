@@ -19,6 +19,9 @@
 
 namespace fwk {
 
+// Bumped with every change of the device code that can move its counters.
+#define FW_KERNEL_REVISION "ring2k-1q"
+
 constexpr int kMaxSchema = 64;
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = 32 * kWarpsPerCta;
@@ -54,6 +57,7 @@ struct WalkArgs {
   int32_t* result;
   unsigned long long* scratch;
   uint64_t qid_base;
+  uint64_t qid_stride;  // global id of query i = qid_base + i * qid_stride
   int32_t d;
   uint32_t tp_thresh;
   float inv_p, inv_q;
@@ -1110,7 +1114,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
     if (first >= a.n) break;
     const long long stop = first + kClaim < a.n ? first + kClaim : a.n;
     for (long long qi = first; qi < stop && !ring.failed; ++qi) {
-      const uint64_t qid = a.qid_base + (uint64_t)qi;
+      const uint64_t qid = a.qid_base + (uint64_t)qi * a.qid_stride;
       const uint32_t qlo = (uint32_t)qid, qhi = (uint32_t)(qid >> 32);
       int32_t* __restrict__ row_out = a.result + qi * D;
       int32_t cur = __ldg(a.starts + qi);

@@ -160,7 +160,7 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   WalkArgs a;
   a.xadj = e->d_xadj; a.adj = e->d_adj; a.weight = e->d_weight; a.label = e->d_label;
   a.V = e->V; a.starts = starts_dev; a.n = n; a.result = result_dev; a.scratch = d_scratch;
-  a.qid_base = p->query_id_base; a.d = p->d;
+  a.qid_base = p->query_id_base; a.qid_stride = p->query_id_stride ? p->query_id_stride : 1; a.d = p->d;
   a.tp_thresh = fw::tp_threshold(p->tp);
   a.inv_p = (float)(1.0 / p->p); a.inv_q = (float)(1.0 / p->q);
   a.n2v_fmax = std::max(1.0f, std::max(a.inv_p, a.inv_q)) * 1.00001f;
@@ -225,6 +225,8 @@ int ensure_cap(T** buf, size_t* cap, size_t need) {
 }
 
 }  // namespace
+
+extern "C" const char* fw_kernel_revision(void) { return FW_KERNEL_REVISION; }
 
 extern "C" int fw_device_count(int* count) {
   fw::clear_error();
@@ -420,7 +422,7 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
     rc = drain(which);
     if (rc) break;
     cudaStream_t st = streams[which];
-    bp.query_id_base = p->query_id_base + (uint64_t)off;
+    bp.query_id_base = p->query_id_base + (uint64_t)off * (p->query_id_stride ? p->query_id_stride : 1);
     cudaError_t err = cudaMemcpyAsync(e->d_starts[which], starts_host + off, (size_t)m * 4, cudaMemcpyHostToDevice, st);
     if (err != cudaSuccess) { rc = fw::fail(FW_ERR_CUDA, "H2D copy failed: %s", cudaGetErrorString(err)); break; }
     rc = enqueue_walk(e, &bp, e->d_starts[which], m, e->d_result[which], st, evs[which][0], evs[which][1], dsc[which], hsc[which]);
@@ -599,7 +601,7 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
   WalkArgs a;
   a.xadj = xadj_dev; a.adj = adj_dev; a.weight = weight_dev; a.label = label_dev;
   a.V = V; a.starts = starts_dev; a.n = n; a.result = result_dev; a.scratch = scratch;
-  a.qid_base = p->query_id_base; a.d = p->d;
+  a.qid_base = p->query_id_base; a.qid_stride = p->query_id_stride ? p->query_id_stride : 1; a.d = p->d;
   a.tp_thresh = fw::tp_threshold(p->tp);
   a.inv_p = (float)(1.0 / p->p); a.inv_q = (float)(1.0 / p->q);
   a.n2v_fmax = std::max(1.0f, std::max(a.inv_p, a.inv_q)) * 1.00001f;

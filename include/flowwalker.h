@@ -65,7 +65,10 @@ typedef struct fw_walk_params {
   int32_t schema_len;
   int32_t group_mode;     /* FW_GROUP_*; 0 selects the default */
   uint64_t seed;          /* Philox key; the reference hard-codes 1337 (include/walker.cuh:1324) */
-  uint64_t query_id_base; /* global id of starts[0]; walk i is keyed by query_id_base + i */
+  uint64_t query_id_base; /* global id of starts[0]; walk i is keyed by query_id_base + i * stride */
+  uint64_t query_id_stride; /* distance between the global ids of consecutive queries; 0 means 1.
+                             * Rank r of R walking the ids r, r+R, r+2R, ... of one job (an
+                             * interleaved shard) passes base = r, stride = R. */
 } fw_walk_params;
 
 typedef struct fw_walk_stats {
@@ -94,6 +97,9 @@ typedef struct fw_rmat_params {
 } fw_rmat_params;
 
 const char* fw_last_error(void);
+/* Revision tag of the walk kernels (changes whenever their code does): profile-derived figures
+ * quoted beside a measurement name the revision they were captured on. */
+const char* fw_kernel_revision(void);
 /* Number of CUDA devices visible to the process. */
 int fw_device_count(int* count);
 

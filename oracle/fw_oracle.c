@@ -285,7 +285,7 @@ int fwo_walk(int64_t V, const void* xadj, int xadj_bits, const int32_t* adj,
              const float* weight, const int32_t* label, int app, int d,
              double tp, double p, double q, const int32_t* schema,
              int schema_len, uint64_t seed, uint64_t query_id_base,
-             int group_mode, const int32_t* starts, int64_t n, int32_t* result,
+             uint64_t query_id_stride, int group_mode, const int32_t* starts, int64_t n, int32_t* result,
              uint64_t* stats, int threads) {
   if (V < 0 || n < 0 || d < 0 || d >= (1 << 28)) return -1;
   if (xadj_bits != 32 && xadj_bits != 64) return -2;
@@ -315,7 +315,7 @@ int fwo_walk(int64_t V, const void* xadj, int xadj_bits, const int32_t* adj,
     uint64_t* my_hist = hist ? (uint64_t*)calloc((size_t)d + 1, 8) : NULL;
 #pragma omp for schedule(dynamic, 64)
     for (int64_t i = 0; i < n; ++i) {
-      int len = walk_one(&c, starts[i], query_id_base + (uint64_t)i,
+      int len = walk_one(&c, starts[i], query_id_base + (uint64_t)i * (query_id_stride ? query_id_stride : 1),
                          result + i * (int64_t)(d + 1), &my_scanned);
       my_steps += (uint64_t)len;
       if (my_hist) my_hist[len]++;

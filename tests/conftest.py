@@ -22,3 +22,15 @@ def _built():
         env.pop("CC", None)
         subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], check=True, env=env)
     yield
+
+
+# Lines a test wants in the record of a run that passes as well (pytest -q hides the output of
+# passing tests): observed statistics of the distribution tests.
+REPORT_LINES = []
+
+
+def pytest_terminal_summary(terminalreporter):
+    if REPORT_LINES:
+        terminalreporter.write_sep("-", "observed statistics")
+        for ln in REPORT_LINES:
+            terminalreporter.write_line(ln)

@@ -20,7 +20,7 @@ def lib():
         vp, i64 = ctypes.c_void_p, ctypes.c_int64
         L.fwo_walk.argtypes = [i64, vp, ctypes.c_int, vp, vp, vp, ctypes.c_int, ctypes.c_int,
                                ctypes.c_double, ctypes.c_double, ctypes.c_double, vp, ctypes.c_int,
-                               ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, vp, i64, vp, vp,
+                               ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int, vp, i64, vp, vp,
                                ctypes.c_int]
         _lib = L
     return _lib
@@ -35,7 +35,7 @@ def philox(ctr, key):
 
 
 def walk(xadj, adj, weight, label, app, starts, d=80, tp=0.2, p=2.0, q=0.5, schema=None,
-         seed=1337, query_id_base=0, group_mode=64, threads=0):
+         seed=1337, query_id_base=0, group_mode=64, threads=0, query_id_stride=1):
     """Returns (result[n, d+1] int32, steps, scanned, len_hist[d+1])."""
     xadj = np.ascontiguousarray(xadj)
     assert xadj.dtype in (np.dtype(np.uint32), np.dtype(np.int64))
@@ -51,7 +51,7 @@ def walk(xadj, adj, weight, label, app, starts, d=80, tp=0.2, p=2.0, q=0.5, sche
                         adj.ctypes.data, None if w is None else w.ctypes.data,
                         None if lb is None else lb.ctypes.data, app, d, tp, p, q,
                         None if sc is None else sc.ctypes.data, 0 if sc is None else len(sc),
-                        seed, query_id_base, group_mode, starts.ctypes.data, n, out.ctypes.data,
+                        seed, query_id_base, query_id_stride, group_mode, starts.ctypes.data, n, out.ctypes.data,
                         stats.ctypes.data, threads)
     if rc != 0:
         raise RuntimeError("fwo_walk failed: %d" % rc)
@@ -142,3 +142,56 @@ def chi_square_transitions(xadj, adj, weight, label, app, walks, min_expected=5.
         dof += len(e_big) - 1
     pval = float(sps.chi2.sf(chi2, dof)) if dof > 0 else 1.0
     return chi2, dof, pval
+
+
+def chi_square_state(xadj, adj, weight, label, app, cur, prev, k, nexts, min_expected=5.0, **kw):
+    """Pearson chi-square of the observed next vertices `nexts` (one per visit of the state
+    cur / prev / step k) against the exact law of that state; vectorised, for states visited
+    millions of times (hub rows).  Cells below `min_expected` are pooled.  Returns (chi2, dof)."""
+    bias = exact_bias(xadj, adj, weight, label, app, cur, prev, k, kw.get("p", 2.0), kw.get("q", 0.5),
+                      kw.get("schema"))
+    b, e = row(xadj, cur)
+    ids, inv = np.unique(adj[b:e], return_inverse=True)          # parallel edges share a cell
+    cell_bias = np.bincount(inv, weights=bias, minlength=len(ids))
+    nexts = np.asarray(nexts)
+    pos = np.minimum(np.searchsorted(ids, nexts), len(ids) - 1)
+    assert (ids[pos] == nexts).all(), "sampled a vertex outside the row"
+    obs = np.bincount(pos, minlength=len(ids)).astype(np.float64)
+    assert (obs[cell_bias <= 0] == 0).all(), "sampled an edge of zero bias"
+    keep = cell_bias > 0
+    exp = len(nexts) * cell_bias[keep] / cell_bias[keep].sum()
+    obs = obs[keep]
+    big = exp >= min_expected
+    e_big, o_big = exp[big], obs[big]
+    if (~big).any():
+        e_big = np.append(e_big, exp[~big].sum())
+        o_big = np.append(o_big, obs[~big].sum())
+    if len(e_big) < 2:
+        return 0.0, 0
+    return float(((o_big - e_big) ** 2 / e_big).sum()), len(e_big) - 1
+
+
+def chi_square_pvalue(chi2, dof):
+    from scipy import stats as sps
+    return float(sps.chi2.sf(chi2, dof)) if dof > 0 else 1.0
+
+
+def length_agreement(la, lb, d, family_level=0.01):
+    """Two samples of walk lengths (same size): per-bin z-scores of the two histograms over the
+    bins that hold at least 20 walks together, the 3-sigma reading of the criterion, and the
+    threshold that keeps the family-wise false-alarm rate of `family_level` over those K bins
+    (Bonferroni: z* = Phi^-1(1 - level / 2K); 3.0 when that is lower).  Returns a dict."""
+    from scipy import stats as sps
+    n = len(la)
+    assert len(lb) == n
+    ha = np.bincount(la, minlength=d + 1).astype(np.float64)
+    hb = np.bincount(lb, minlength=d + 1).astype(np.float64)
+    pooled = (ha + hb) / (2.0 * n)
+    sigma = np.sqrt(pooled * (1 - pooled) * 2.0 / n)
+    big = (ha + hb) >= 20
+    z = (ha[big] - hb[big]) / n / sigma[big]
+    K = int(big.sum())
+    zstar = max(3.0, float(sps.norm.isf(family_level / (2.0 * max(K, 1)))))
+    mean_z = abs(la.mean() - lb.mean()) / (np.sqrt((la.var() + lb.var()) / n) + 1e-300)
+    return {"bins": K, "max_abs_z": float(np.abs(z).max()) if K else 0.0, "threshold": zstar,
+            "beyond_3_sigma": int((np.abs(z) > 3.0).sum()), "mean_z": float(mean_z)}

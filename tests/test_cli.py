@@ -122,6 +122,10 @@ def test_cli_two_gpus_and_int64_offsets(tmp_path):
     r = run("--input", prefix, "--deepwalk", "--all", "--d", "12", "--shards", "3", "--save_result", out3)
     assert r.returncode == 0, r.stdout + r.stderr
     assert (np.fromfile(out3, dtype=np.int32).reshape(g.V, 13) == ref).all()
+    r = run("--input", prefix, "--deepwalk", "--all", "--d", "12", "--shards", "3", "--interleave",
+            "--save_result", out3)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert (np.fromfile(out3, dtype=np.int32).reshape(g.V, 13) == ref).all()
     if n_dev.value < 2:
         pytest.skip("one visible device: the two-device half of this test needs two")
     out2 = str(tmp_path / "w2.bin")

@@ -134,6 +134,13 @@ def test_shards_union_equals_single_run():
     a, _ = eng.walk(fw.make_params(fw.APP_DEEPWALK, d=40, query_id_base=0), starts[:500])
     b, _ = eng.walk(fw.make_params(fw.APP_DEEPWALK, d=40, query_id_base=500), starts[500:])
     assert (np.vstack([a, b]) == full).all()
+    # interleaved shards: rank r of 3 walks the ids r, r + 3, ... (query_id_stride)
+    for r in range(3):
+        part, _ = eng.walk(fw.make_params(fw.APP_DEEPWALK, d=40, query_id_base=r, query_id_stride=3), starts[r::3])
+        assert (part == full[r::3]).all()
+    strided, _ = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40, query_id_base=1, query_id_stride=3),
+                                starts[1::3], batch_size=100)
+    assert (strided == full[1::3]).all()
     out, st = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=128)
     assert (out == full).all() and st.launches == 8
     auto, st_auto = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=0)  # autobatch

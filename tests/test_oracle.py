@@ -169,3 +169,37 @@ def test_edge_cases():
     a = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], None, 0, starts[:50], d=6, query_id_base=0)[0]
     b = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], None, 0, starts[50:], d=6, query_id_base=50)[0]
     assert (np.vstack([a, b]) == r32).all()
+
+
+def test_hub_law_helpers_on_the_golden_walker():
+    """The vectorised chi-square used for hub rows and the walk-length comparison, exercised on the
+    golden walker itself: a 3,000-neighbour row with weights over two decades (DeepWalk and, arriving
+    from a neighbour, node2vec), and two independent PPR runs whose lengths must agree."""
+    rng = np.random.default_rng(3)
+    V = 3001
+    rows = [np.arange(1, V)] + [np.unique(np.concatenate([[0], rng.integers(1, V, 2)])) for _ in range(1, V)]
+    arrs = graphs.from_rows(rows, V=V, rng=rng)
+    arrs["weight"][:V - 1] = (10.0 ** rng.uniform(-1.3, 0.7, V - 1)).astype(np.float32)
+    n = 300000
+    walks = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], 0, np.zeros(n, np.int32), d=1)[0]
+    chi2, dof = O.chi_square_state(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], 0, 0, -1, 0, walks[:, 1])
+    assert dof > 2000 and O.chi_square_pvalue(chi2, dof) > 0.001
+    # a wrong law (uniform weights) must be rejected by the same statistic
+    chi2u, dofu = O.chi_square_state(arrs["xadj"], arrs["adj"], np.ones_like(arrs["weight"]), arrs["label"], 0, 0, -1,
+                                     0, walks[:, 1])
+    assert O.chi_square_pvalue(chi2u, dofu) < 1e-6
+    leaf = 7
+    w2 = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], 2, np.full(n, leaf, np.int32), d=2,
+                p=2.0, q=0.5)[0]
+    sel = (w2[:, 1] == 0) & (w2[:, 2] >= 0)
+    chi2, dof = O.chi_square_state(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], 2, 0, leaf, 1,
+                                   w2[sel, 2], p=2.0, q=0.5)
+    assert dof > 1000 and O.chi_square_pvalue(chi2, dof) > 0.001
+    g = graphs.config1()
+    starts = graphs.config1_starts(200000, seed=8)
+    la = (O.graph_walk(g, 1, starts, d=80, tp=0.2, seed=1)[0][:, 1:] >= 0).sum(axis=1)
+    lb = (O.graph_walk(g, 1, starts, d=80, tp=0.2, seed=2)[0][:, 1:] >= 0).sum(axis=1)
+    r = O.length_agreement(la, lb, 80)
+    assert r["bins"] > 10 and r["max_abs_z"] < r["threshold"] and 3.0 <= r["threshold"] < 4.0 and r["mean_z"] < 4.0
+    shifted = O.length_agreement(la, np.minimum(lb + (np.arange(len(lb)) % 10 == 0), 80), 80)
+    assert shifted["max_abs_z"] > shifted["threshold"]

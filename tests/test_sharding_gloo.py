@@ -31,6 +31,12 @@ def _worker(rank, world, port, tmpdir):
     starts = graphs.config1_starts(301)
     lo, hi = multi.shard_range(len(starts), rank, world)
     res, steps, scanned, _ = O.graph_walk(g, 0, starts[lo:hi], d=20, query_id_base=lo)
+    # the interleaved assignment (ids rank, rank + world, ...) gives the same rows
+    inter = O.graph_walk(g, 0, starts[rank::world], d=20, query_id_base=rank, query_id_stride=world)[0]
+    full_ids = np.arange(len(starts))
+    mine = full_ids[rank::world]
+    in_range = (mine >= lo) & (mine < hi)
+    assert (inter[in_range] == res[mine[in_range] - lo]).all()
     (tot_steps, tot_scanned), (tmax,) = multi.reduce_counters(dist, [steps, scanned], [10.0 + rank])
     allrows = multi.gather_rows(dist, res, len(starts), rank, world)
     if rank == 0:
