@@ -20,12 +20,23 @@
 namespace fwk {
 
 // Bumped with every change of the device code that can move its counters.
-#define FW_KERNEL_REVISION "ring2k-1q"
+#define FW_KERNEL_REVISION "stream4k-slots"
 
 constexpr int kMaxSchema = 64;
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = 32 * kWarpsPerCta;
-constexpr int kClaim = 4;                // queries claimed per atomic
+#ifndef FW_SLOTS
+#define FW_SLOTS 8
+#endif
+#ifndef FW_N2V_SLOTS
+#define FW_N2V_SLOTS 1
+#endif
+// Queries in flight per warp (slot i lives in the registers of lane i), by the kernel's app.
+template <int APP>
+__host__ __device__ constexpr int slots_of() {
+  return APP == FW_APP_NODE2VEC ? FW_N2V_SLOTS : FW_SLOTS;
+}
+constexpr int kMinClaim = 4;             // queries claimed per atomic, at least
 constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared memory up to this d+1
 #ifndef FW_STAGES
 #define FW_STAGES 2
@@ -34,7 +45,7 @@ constexpr int kMaxSmemHist = 8192;       // walk-length histogram kept in shared
 #define FW_N2V_MIN_BLOCKS 4
 #endif
 #ifndef FW_MIN_BLOCKS
-#define FW_MIN_BLOCKS 5
+#define FW_MIN_BLOCKS 3
 #endif
 constexpr int kStages = FW_STAGES;       // ring depth per warp
 constexpr uint32_t kSubBytes = 16u * fw::kQuadsPerSub;  // 2 KB: one ring stage, one bulk copy
@@ -42,6 +53,17 @@ constexpr uint32_t kSubBytes = 16u * fw::kQuadsPerSub;  // 2 KB: one ring stage,
 template <int APP>
 __host__ __device__ constexpr bool uses_ring() { return true; }
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls of an mbarrier before giving up
+
+// Build with -DFW_PHASE_TIMERS to make every warp add up the clock cycles it spends in each part
+// of its loop (a development aid: where the warps sit, not what the SM is busy with).
+#ifdef FW_PHASE_TIMERS
+#define FW_PROF(...) __VA_ARGS__
+// 0 short-row picks, 1 direct, 2 ring (cycles); 3..5 their counts; 6 sub-blocks of ring rows;
+// 7 in-strip picks of long rows (cycles); 8 everything outside the picks (cycles); 9 warp lifetime
+static __device__ unsigned long long g_prof[16];
+#else
+#define FW_PROF(...)
+#endif
 
 // Scratch words (uint64) in device memory.
 constexpr int kSlotSteps = 0, kSlotScanned = 1, kSlotStatus = 2, kSlotCounter = 3, kSlotHist = 4;
@@ -121,6 +143,38 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < kWaitLimit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
+}
+
+// The same bounded wait as one block of PTX: in the usual case (the copy has landed) it costs the
+// test and one taken branch, and the compiler sees no control flow to protect.  1 when the
+// phase completed, 0 when kWaitLimit polls went by.
+__device__ __forceinline__ uint32_t mbar_wait_inline(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n\t"
+      "FW_WAIT:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra FW_DONE;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 p, n, %3;\n\t"
+      "@p bra FW_WAIT;\n\t"
+      "FW_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kWaitLimit)
+      : "memory");
+  return ok;
+}
+// expect-tx + bulk copy under a predicate instead of a branch (`go` != 0 in one lane at most)
+__device__ __forceinline__ void bulk_g2s_if(uint32_t go, uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %4, 0;\n\t"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %2;\n\t"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar), "r"(go)
+      : "memory");
 }
 
 // ---- bias of one quad ----
@@ -472,6 +526,91 @@ __device__ __forceinline__ bool ring_sub(const WalkArgs& a, const StepCtx& c, ui
   return true;
 }
 
+// ---- the sweep of DeepWalk, PPR and MetaPath: two stages of half a supergroup (4 KB) each ----
+//
+// A warp sweeping a row is one chain of dependent steps per staged copy: wait, load from shared
+// memory, add, hand the stage back.  The SM's throughput on long rows is (warps) x (bytes per
+// chain) / (latency of the chain), so the stage is made large -- one bulk copy, one wait and one
+// refill per 4 KB, the eight 128-bit loads and the thirty adds of a stage independent of one
+// another -- and every row of more than 32 quads goes through the ring from its first quad to its
+// last: half h of the row (quads 256 h .. 256 h + 255, the last one as far as the row goes)
+// sits in stage h mod 2, supergroup s is halves 2s and 2s+1.  Both stages are filled when the
+// row starts, so a row of up to 2,048 neighbours is one round trip to memory, whatever its
+// length, and is still in shared memory when the pick inside the winning strip needs it.  The
+// row's first and last supergroup are reduced with the boundary masks, the ones in between bare.
+constexpr uint32_t kHalfBytes = 2u * kSubBytes;      // one stage
+constexpr uint32_t kHalfQuads = 2u * fw::kQuadsPerSub;
+
+// Ring bytes per warp by the kernel's app: node2vec keeps the ring of two 2 KB stages.
+template <int APP>
+__host__ __device__ constexpr uint32_t ring_bytes() {
+  return APP == FW_APP_NODE2VEC ? (uint32_t)kStages * kSubBytes : 2u * kHalfBytes;
+}
+
+// Bytes of half h of a row of nq quads.
+__device__ __forceinline__ uint32_t half_bytes(uint32_t nq, uint32_t h) {
+  return 16u * min(kHalfQuads, nq - kHalfQuads * h);
+}
+
+// Half h of the row into its stage (lane 0 only calls this; h < number of halves).
+__device__ __forceinline__ void half_fill(const StepCtx& c, const Ring& ring, uint32_t h) {
+  const uint32_t T = h & 1u, bytes = half_bytes(c.nq, h);
+  mbar_expect_tx(ring.bar + 8u * T, bytes);
+  bulk_g2s(ring.data + T * kHalfBytes, c.prim + (size_t)h * kHalfQuads, bytes, ring.bar + 8u * T);
+}
+
+// Half 2s + T of the row from stage T: the lane's two partial sums (one per sub-block), then the
+// stage is handed back with half 2s + T + 2 (while that one is below h_end) by lane 0 alone, and
+// only once its own sums exist: a shared-memory load delivers all lanes' values together, so the
+// warp has read the whole stage by then.  (The sums are >= 0 always; the test is there to make
+// the refill depend on the loads.)  EDGE: the supergroup holds the row's first or last quad --
+// quads outside the row (stale bytes of the stage included) are masked, and a half that does
+// not exist counts as zero, which leaves the strip's total as the shorter sum would give it.
+// `lane_ptr` = the warp's stage 0 + 16 * lane.  Returns 0 when the wait ran out.
+template <int APP, bool CLEAN, int T, bool EDGE>
+__device__ __forceinline__ uint32_t half_take(const StepCtx& c, uint32_t s, uint32_t n_half, uint32_t h_end,
+                                              uint32_t lane, const Ring& ring, const int4* lane_ptr, uint32_t& parity,
+                                              float& Alo, float& Ahi) {
+  const uint32_t h = 2u * s + T;
+  if (EDGE && h >= n_half) {  // warp-uniform
+    Alo = 0.0f;
+    Ahi = 0.0f;
+    return 1u;
+  }
+  const uint32_t bar = ring.bar + 8u * T;
+  const uint32_t ok = mbar_wait_inline(bar, (parity >> T) & 1u);
+  parity ^= 1u << T;
+  const int4* st = lane_ptr + T * kHalfQuads;
+  int4 raw[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) raw[j] = st[32 * j];
+  float S[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float4 v = plain_bias<APP, CLEAN>(raw[j], c.want);
+    if (EDGE) mask_quad(v, kHalfQuads * h + 32u * j + lane, c.head, c.tail);
+    S[j] = sum4(v);
+  }
+  Alo = sum_strip(S);
+  Ahi = sum_strip(S + 4);
+  const uint32_t go = (lane == 0u && h + 2u < h_end && Alo >= 0.0f && Ahi >= 0.0f) ? ok : 0u;
+  bulk_g2s_if(go, ring.data + T * kHalfBytes, c.prim + (size_t)(h + 2u) * kHalfQuads, half_bytes(c.nq, h + 2u), bar);
+  return ok;
+}
+
+// One whole supergroup s: both stages, the strip's total in the canonical order (A0+A1)+(A2+A3).
+// False when a staged copy did not arrive (looked at once per supergroup: until then the sums
+// are formed from whatever the stage holds and dropped, and nothing is refilled).
+template <int APP, bool CLEAN, bool EDGE>
+__device__ __forceinline__ bool super_turn(const StepCtx& c, uint32_t s, uint32_t n_half, uint32_t h_end,
+                                           uint32_t lane, Ring& ring, const int4* lane_ptr, float& W) {
+  float A0, A1, A2, A3;
+  uint32_t ok = half_take<APP, CLEAN, 0, EDGE>(c, s, n_half, h_end, lane, ring, lane_ptr, ring.parity, A0, A1);
+  ok &= half_take<APP, CLEAN, 1, EDGE>(c, s, n_half, h_end, lane, ring, lane_ptr, ring.parity, A2, A3);
+  W = __fadd_rn(__fadd_rn(A0, A1), __fadd_rn(A2, A3));
+  return __all_sync(0xFFFFFFFFu, ok != 0u);
+}
+
 // ---- node2vec: sweep with the membership test only where it can matter ----
 //
 // bias = w * f with f in {1/p, 1, 1/q}, so a strip's total bias W is at most fmax * sum(w) and
@@ -625,67 +764,61 @@ __device__ __forceinline__ void absorb(const WalkArgs& a, const StepCtx& c, Supe
   }
 }
 
-// Inverse-CDF pick inside the winning strip B (every lane computes the same): the first of
-// its edges in canonical order (quad j, edge k) whose running sum exceeds u * W, u from the pick
-// word.  Zero biases leave the running sum unchanged, so counting the sums <= u * W gives that
-// edge's position.  Returns the edge index relative to quad 0 of the row.
+// The same for a whole supergroup s whose total W is already formed (never the row's last one).
 template <int APP, bool CLEAN>
+__device__ __forceinline__ void absorb_super(const WalkArgs& a, const StepCtx& c, SuperAcc& s, Best& best, float W,
+                                             uint32_t sg, bool last, uint32_t lane, uint32_t c1, uint32_t qlo,
+                                             uint32_t qhi) {
+  const uint32_t x = s.m == 0u ? s.r.x : s.m == 1u ? s.r.y : s.r.z;
+  if (APP == FW_APP_NODE2VEC && c.prev >= 0) n2v_test<CLEAN>(a, c, sg, lane, W, x, s.r.w, best);
+  else offer_filtered(best, x, s.r.w, W, sg * 32u + lane, __uint_as_float(__reduce_min_sync(0xFFFFFFFFu, best.key)));
+  if (!last && ++s.m == 3u) { s.m = 0u; s.r = fw::philox4x32_10((++s.g) * 32u + lane, c1, qlo, qhi, a.k0, a.k1); }
+}
+
+// Inverse-CDF pick inside the winning strip B: the first of its edges in canonical order (quad j,
+// edge k) whose running sum exceeds u * W, u from the pick word.  Zero biases leave the running
+// sum unchanged, so counting the sums <= u * W gives that edge's position.  The strip's (up to)
+// sixteen quads are loaded side by side, one per lane, and the running sum then walks over them
+// by shuffles in the canonical order: one memory round trip instead of one per quad.  Plain
+// biases only (node2vec picks with n2v_pick).  Returns the edge index relative to quad 0 of the row.
+template <int APP, bool CLEAN, bool FROM_RING = false>
 __device__ __forceinline__ uint32_t pick_in_row(const WalkArgs& a, const StepCtx& c, uint32_t B, uint32_t pick,
-                                                float W, uint32_t lane) {
+                                                float W, uint32_t lane, const unsigned char* ring_ptr = nullptr) {
+  static_assert(APP != FW_APP_NODE2VEC, "node2vec's pick needs the membership test: n2v_pick");
   const uint32_t sB = B >> 5, lB = B & 31u;
   const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
   const uint32_t last_blk = (c.nq - 1u) >> 5;
   const uint32_t blk0 = 16u * sB;
   const uint32_t nblk = min(16u, last_blk - blk0 + 1u);
-  if (APP == FW_APP_NODE2VEC) c.from = 0u;  // the strip may lie before the blocks just visited
+  const uint32_t q = 32u * (blk0 + lane) + lB;  // lane j holds the strip's quad j
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (lane < nblk && q < c.nq) {
+    // FROM_RING: the row is one supergroup at most and still staged (quad q at 16 q of the ring)
+    const int4 raw = FROM_RING ? reinterpret_cast<const int4*>(ring_ptr)[q] : __ldg(c.prim + q);
+    v = plain_bias<APP, CLEAN>(raw, c.want);
+    mask_quad(v, q, c.head, c.tail);
+  }
   float acc = 0.0f;
   uint32_t cnt = 0, j = 0;
 #pragma unroll 1
   for (; j < nblk; ++j) {
-    const uint32_t blk = blk0 + j;
-    const bool edge_blk = blk == 0u || blk == last_blk;
-    float4 v;
-    if (APP == FW_APP_NODE2VEC) {
-      // the membership test works on whole blocks: load the block as a warp, take lane lB's quad
-      v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
-      v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
-      v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
-      v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
-      v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
-    } else {
-      v = block_quad<APP, CLEAN>(a, c, blk, last_blk, lB);
-    }
+    const float x = __shfl_sync(0xFFFFFFFFu, v.x, (int)j), y = __shfl_sync(0xFFFFFFFFu, v.y, (int)j);
+    const float z = __shfl_sync(0xFFFFFFFFu, v.z, (int)j), w = __shfl_sync(0xFFFFFFFFu, v.w, (int)j);
     // biases are >= 0, so the running sums never decrease: when the quad's last sum is still
     // <= thr all four are, and the quad is passed with one comparison
-    const float p0 = __fadd_rn(acc, v.x), p1 = __fadd_rn(p0, v.y), p2 = __fadd_rn(p1, v.z);
-    acc = __fadd_rn(p2, v.w);
+    const float p0 = __fadd_rn(acc, x), p1 = __fadd_rn(p0, y), p2 = __fadd_rn(p1, z);
+    acc = __fadd_rn(p2, w);
     if (acc <= thr) { cnt += 4u; continue; }
     cnt += (p0 <= thr ? 1u : 0u) + (p1 <= thr ? 1u : 0u) + (p2 <= thr ? 1u : 0u);
     break;  // found (warp-uniform)
   }
   if (j == nblk) {
     // rounding pushed u * W past the sequential total: take the strip's last positive edge
-    if (APP == FW_APP_NODE2VEC) c.from = 0u;
-    cnt = 0;
-#pragma unroll 1
-    for (j = 0; j < nblk; ++j) {
-      const uint32_t blk = blk0 + j;
-      const bool edge_blk = blk == 0u || blk == last_blk;
-      float4 v;
-      if (APP == FW_APP_NODE2VEC) {
-        v = load_quad<APP, CLEAN>(a, c, 32u * blk + lane, edge_blk);
-        v.x = __shfl_sync(0xFFFFFFFFu, v.x, (int)lB);
-        v.y = __shfl_sync(0xFFFFFFFFu, v.y, (int)lB);
-        v.z = __shfl_sync(0xFFFFFFFFu, v.z, (int)lB);
-        v.w = __shfl_sync(0xFFFFFFFFu, v.w, (int)lB);
-      } else {
-        v = block_quad<APP, CLEAN>(a, c, blk, last_blk, lB);
-      }
-      if (v.x > 0.0f) cnt = 4u * j;
-      if (v.y > 0.0f) cnt = 4u * j + 1u;
-      if (v.z > 0.0f) cnt = 4u * j + 2u;
-      if (v.w > 0.0f) cnt = 4u * j + 3u;
-    }
+    const uint32_t m = (v.x > 0.0f ? 1u : 0u) | (v.y > 0.0f ? 2u : 0u) | (v.z > 0.0f ? 4u : 0u) | (v.w > 0.0f ? 8u : 0u);
+    const uint32_t have = __ballot_sync(0xFFFFFFFFu, m != 0u);
+    const int top = have ? 31 - __clz((int)have) : 0;
+    const uint32_t mt = __shfl_sync(0xFFFFFFFFu, m, top);
+    cnt = have ? 4u * (uint32_t)top + (uint32_t)(31 - __clz((int)mt)) : 0u;
   }
   return 4u * (32u * (blk0 + (cnt >> 2)) + lB) + (cnt & 3u);
 }
@@ -734,25 +867,35 @@ template <int APP, bool CLEAN>
 __device__ __forceinline__ bool sweep_supers(const WalkArgs& a, const StepCtx& c, uint32_t s0, uint32_t s1,
                                              uint32_t lane, uint32_t c1, uint32_t qlo, uint32_t qhi, Ring& ring,
                                              const unsigned char* ring_ptr, Best& best) {
-  const uint32_t b0 = 4u * s0, bend = 4u * s1;
-  if (uses_ring<APP>() && lane == 0) {
-#pragma unroll
-    for (uint32_t t = 0; t < kStages; ++t)
-      if (b0 + t < bend) ring_fill<SweepApp<APP>::value>(c, ring, b0 + t, t);
-  }
   SuperAcc acc{0.0f, 0.0f, s0 / 3u, s0 % 3u, fw::Philox4{0u, 0u, 0u, 0u}};
   acc.r = fw::philox4x32_10(acc.g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
-  uint32_t t = 0;
+  if constexpr (APP == FW_APP_NODE2VEC) {
+    const uint32_t b0 = 4u * s0, bend = 4u * s1;
+    if (lane == 0) {
+#pragma unroll
+      for (uint32_t t = 0; t < kStages; ++t)
+        if (b0 + t < bend) ring_fill<SweepApp<APP>::value>(c, ring, b0 + t, t);
+    }
+    uint32_t t = 0;
 #pragma unroll 1
-  for (uint32_t b = b0; b < bend; ++b) {
-    float A;
-    if (uses_ring<APP>()) {
+    for (uint32_t b = b0; b < bend; ++b) {
+      float A;
       if (!ring_sub<SweepApp<APP>::value, CLEAN>(a, c, b, bend, lane, ring, ring_ptr, t, A)) return false;
       t = t + 1u == (uint32_t)kStages ? 0u : t + 1u;
-    } else {
-      A = sub_global<SweepApp<APP>::value, CLEAN>(a, c, b, lane);
+      absorb<APP, CLEAN>(a, c, acc, best, A, b, false, true, lane, c1, qlo, qhi);
     }
-    absorb<APP, CLEAN>(a, c, acc, best, A, b, false, true, lane, c1, qlo, qhi);
+  } else {
+    if (lane == 0) {
+      half_fill(c, ring, 2u * s0);
+      half_fill(c, ring, 2u * s0 + 1u);
+    }
+    const int4* lane_ptr = reinterpret_cast<const int4*>(ring_ptr) + lane;
+#pragma unroll 1
+    for (uint32_t s = s0; s < s1; ++s) {
+      float W;
+      if (!super_turn<SweepApp<APP>::value, CLEAN, false>(c, s, 2u * s1, 2u * s1, lane, ring, lane_ptr, W)) return false;
+      absorb_super<APP, CLEAN>(a, c, acc, best, W, s, false, lane, c1, qlo, qhi);
+    }
   }
   return true;
 }
@@ -905,6 +1048,89 @@ __device__ __noinline__ unsigned long long strip_redo(const WalkArgs& args, Step
   return ((unsigned long long)pick << 32) | __float_as_uint(W);
 }
 
+// The strip sampler of DeepWalk, PPR and MetaPath on a row of more than 32 quads: the whole row
+// streams through the warp's two 4 KB stages (see half_take).  `r0`: the lane's first Philox block.
+template <int APP, int MODE, bool CLEAN>
+__device__ __forceinline__ uint32_t sweep_streamed(const WalkArgs& a, const StepCtx& c, uint32_t c1, uint32_t qlo,
+                                                   uint32_t qhi, uint32_t lane, Ring& ring, const unsigned char* ring_ptr,
+                                                   CoopTask* task, const fw::Philox4& r0) {
+  constexpr int SAPP = SweepApp<APP, MODE>::value;
+  Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
+  const uint32_t n_half = (c.nq + kHalfQuads - 1u) / kHalfQuads;
+  const uint32_t end_super = ((n_half + 1u) >> 1) - 1u;  // the row's last supergroup
+  if (lane == 0) {
+    half_fill(c, ring, 0u);
+    if (n_half > 1u) half_fill(c, ring, 1u);
+  }
+  SuperAcc acc{0.0f, 0.0f, 0u, 0u, r0};
+  // A very long row is posted for the CTA's idle warps, which take supergroups from the back.
+  bool posted = false;
+  if (MODE == kModeStripShared && end_super + 1u >= kCoopMinSupers)
+    posted = coop_post(task, c.prim, c.sec, c.nq, c.head, c.tail, c.prev, c.prow, c.plen, c.want, c1, qlo, qhi,
+                       end_super, lane) != 0u;
+  uint32_t tickets = 0;
+  bool stopped = false;
+  const int4* lane_ptr = reinterpret_cast<const int4*>(ring_ptr) + lane;
+  uint32_t sg = 0;
+#pragma unroll 1
+  for (;;) {
+    const bool last = sg == end_super;
+    float W;
+    bool ok;
+    if (sg == 0u || last) ok = super_turn<SAPP, CLEAN, true>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
+    else ok = super_turn<SAPP, CLEAN, false>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
+    if (!ok) { ring.failed = true; return 0xFFFFFFFFu; }
+    absorb_super<APP, CLEAN>(a, c, acc, best, W, sg, last, lane, c1, qlo, qhi);
+    if (last) break;
+    ++sg;
+    if (posted && sg < end_super) {
+      // this warp stops in front of the supergroups the drawn tickets cover
+      unsigned int k = 0;
+      if (lane == 0) k = ld_volatile(&task->ticket) & 0xFFFFu;
+      if (sg + __shfl_sync(0xFFFFFFFFu, k, 0) * kCoopChunkSupers >= end_super) {
+        // hand-over: both halves of supergroup sg are in flight or staged; wait for them, drop
+        // them, and go on with the row's last supergroup, which stays with this warp
+        tickets = coop_stop_tickets(task, lane);
+        stopped = true;
+        bool arrived = mbar_wait(ring.bar, ring.parity & 1u);
+        arrived = mbar_wait(ring.bar + 8u, (ring.parity >> 1) & 1u) && arrived;
+        ring.parity ^= 3u;
+        if (!__all_sync(0xFFFFFFFFu, arrived)) { ring.failed = true; return 0xFFFFFFFFu; }
+        sg = end_super;
+        if (lane == 0) {
+          half_fill(c, ring, 2u * sg);
+          if (2u * sg + 1u < n_half) half_fill(c, ring, 2u * sg + 1u);
+        }
+        acc.g = sg / 3u;
+        acc.m = sg - 3u * acc.g;
+        acc.r = fw::philox4x32_10(acc.g * 32u + lane, c1, qlo, qhi, a.k0, a.k1);
+      }
+    }
+  }
+  if (posted && !stopped) tickets = coop_stop_tickets(task, lane);
+  warp_argmin(best.key, best.id);
+  uint32_t B = best.id;
+  if (posted) {
+    const unsigned long long own = ((unsigned long long)best.key << 32) | best.id;
+    const unsigned long long fin = coop_close(task, tickets, own, lane);
+    if (fin == kCoopFailed) { ring.failed = true; return 0xFFFFFFFFu; }
+    B = (uint32_t)fin;
+    if (B != 0xFFFFFFFFu && fin != own) {  // another warp reduced the winning strip
+      const unsigned long long pw = strip_redo<APP, CLEAN>(a, c, B, c1, qlo, qhi, lane);
+      return pick_in_row<SAPP, CLEAN>(a, c, B, (uint32_t)(pw >> 32), __uint_as_float((uint32_t)pw), lane);
+    }
+  }
+  if (B == 0xFFFFFFFFu) return B;
+  FW_PROF(const long long tp0 = clock64();)
+  const uint32_t pick = __shfl_sync(0xFFFFFFFFu, best.pick, (int)(B & 31u));
+  const float WB = __shfl_sync(0xFFFFFFFFu, best.W, (int)(B & 31u));
+  // a row of one supergroup is still in the ring
+  const uint32_t rel = end_super == 0u ? pick_in_row<SAPP, CLEAN, true>(a, c, B, pick, WB, lane, ring_ptr)
+                                       : pick_in_row<SAPP, CLEAN>(a, c, B, pick, WB, lane);
+  FW_PROF(if (lane == 0) atomicAdd(&g_prof[7], (unsigned long long)(clock64() - tp0));)
+  return rel;
+}
+
 // One weighted pick in the row described by c, by one warp.  Returns the
 // edge index relative to quad 0 of the row, or 0xFFFFFFFF when no edge has
 // positive bias.
@@ -969,13 +1195,15 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     return 4u * (uint32_t)src + cnt;
   }
 
-  // The row is swept in sub-blocks of 128 quads (2 KB): the first and the last straight from
-  // global memory (boundary quads, partial fill), the interior ones through the ring when
-  // there are any.  Four sub-blocks make a supergroup; a lane's four partial sums A0..A3 are
-  // combined as (A0+A1)+(A2+A3) and tested once per supergroup.
+  if constexpr (APP != FW_APP_NODE2VEC) return sweep_streamed<APP, MODE, CLEAN>(a, c, c1, qlo, qhi, lane, ring, ring_ptr, task, r);
+
+  // node2vec.  The row is swept in sub-blocks of 128 quads (2 KB): the first and the last straight
+  // from global memory (boundary quads, partial fill), the interior ones through a ring of two
+  // 2 KB stages when there are any.  Four sub-blocks make a supergroup; a lane's four partial
+  // sums A0..A3 are combined as (A0+A1)+(A2+A3) and tested once per supergroup.
   const uint32_t nb = (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;
   const uint32_t last_b = nb - 1u;
-  const bool ringed = uses_ring<APP>() && nb >= 3u;
+  const bool ringed = nb >= 3u;
   if (ringed && lane == 0) {
 #pragma unroll
     for (uint32_t t = 0; t < kStages; ++t)
@@ -1004,8 +1232,10 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
     }
   } else {
     uint32_t t = 0;
-    // Kept rolled on purpose: an unrolled sweep measured slower (instruction cache shared by
-    // 40 warps that sit at different places of the kernel).
+    // Kept rolled on purpose: an unrolled sweep measured slower (instruction cache shared by the
+    // warps of an SM, which sit at different places of the kernel), and node2vec's key test is
+    // large: a second copy of it in a leaner loop cost more than the loop saved (157 against
+    // 107 ms on R-MAT scale 20, edge factor 32).
 #pragma unroll 1
     for (; b < last_b; ++b) {
       if (posted && (b & 3u) == 0u && taken(b)) {
@@ -1064,11 +1294,10 @@ __device__ __forceinline__ uint32_t sample_row_warp(const WalkArgs& a, const Ste
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
 constexpr int min_blocks() {
-  // Six CTAs of 256 threads per SM need at most 40 registers per thread.  DeepWalk and PPR fit
-  // by themselves; small source changes move the 32-bit MetaPath kernel between 38 and 45, so
-  // it is held to the limit; 64-bit offsets and node2vec need more registers.
-  return MODE == FW_GROUP_EDGE ? 2 : APP == FW_APP_NODE2VEC ? FW_N2V_MIN_BLOCKS
-       : (APP == FW_APP_METAPATH && MODE == FW_GROUP_STRIP && sizeof(OffT) == 4) ? 6 : FW_MIN_BLOCKS;
+  // Resident CTAs of 256 threads per SM the register allocation is held to (65,536 registers:
+  // 3 CTAs -> 85 per thread, 4 -> 64, 5 -> 48).  The strip kernels of DeepWalk, PPR and MetaPath
+  // hold 8 KB of staging ring per warp, so three CTAs per SM is what shared memory allows as well.
+  return MODE == FW_GROUP_EDGE ? 2 : APP == FW_APP_NODE2VEC ? FW_N2V_MIN_BLOCKS : FW_MIN_BLOCKS;
 }
 
 template <int APP, int MODE, bool CLEAN, typename OffT>
@@ -1077,7 +1306,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE ? kStages * stage_bytes<SweepApp<APP, MODE>::value>() : 0u;
+  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE ? ring_bytes<APP>() : 0u;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
   Ring ring;
@@ -1107,59 +1336,148 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
   unsigned long long my_steps = 0, my_scanned = 0;
   uint32_t status = 0;
 
+  // A warp keeps kSlots queries in flight.  The state of slot i (the role of the reference's Task,
+  // include/gpu_task.cuh:24-78) lives in the registers of lane i, so everything that is one
+  // dependent memory access per query -- the start vertex, the row bounds of the current vertex,
+  // the chosen neighbour, the result cell, the stop test -- is issued for all slots by one
+  // instruction and the round trips of the slots overlap.  Only the weighted pick itself takes
+  // the whole warp, one slot after the other.
+  constexpr uint32_t kNone = 0xFFFFFFFFu;
+  constexpr int kSlots = slots_of<APP>();
+  constexpr int kClaim = 2 * kSlots > kMinClaim ? 2 * kSlots : kMinClaim;  // queries claimed per atomic
+  const bool slot_lane = lane < (uint32_t)kSlots;
+  long long qi = -1;                 // index of the slot's query in this launch
+  uint32_t qlo = 0, qhi = 0;         // its global id (key of the random stream)
+  int32_t cur = 0, prev = -1, k = 0; // current and previous vertex, steps taken
+  OffT rb = 0, pb = 0;               // first edge of the current and of the previous vertex's row
+  uint32_t rlen = 0, plen = 0;       // their lengths
+  uint32_t st = 0;                   // 0: empty, 1: walking, 2: walk over, to be closed
+  uint32_t my_rel = kNone;           // the pick of this round
+  long long res_next = 0, res_end = 0;  // queries claimed by the warp and not yet handed to a slot
+  bool exhausted = false;
+
+  FW_PROF(unsigned long long prof_t[3] = {0, 0, 0}, prof_n[3] = {0, 0, 0}, prof_sub = 0; const long long prof_begin = clock64();)
   while (!ring.failed) {
-    long long first = 0;
-    if (lane == 0) first = (long long)atomicAdd(a.scratch + kSlotCounter, (unsigned long long)kClaim);
-    first = __shfl_sync(0xFFFFFFFFu, first, 0);
-    if (first >= a.n) break;
-    const long long stop = first + kClaim < a.n ? first + kClaim : a.n;
-    for (long long qi = first; qi < stop && !ring.failed; ++qi) {
-      const uint64_t qid = a.qid_base + (uint64_t)qi * a.qid_stride;
-      const uint32_t qlo = (uint32_t)qid, qhi = (uint32_t)(qid >> 32);
-      int32_t* __restrict__ row_out = a.result + qi * D;
-      int32_t cur = __ldg(a.starts + qi);
-      if (lane == 0) row_out[0] = cur;
-      StepCtx c;
-      c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = &s_flags[warp][0];
-      int k = 0;
-      if (cur < 0 || (int64_t)cur >= a.V) {
-        status |= FW_STATUS_BAD_START;
-      } else {
-        while (k < a.d) {
-          const int64_t b = (int64_t)__ldg(xadj + cur), e = (int64_t)__ldg(xadj + cur + 1);
-          if (e <= b) break;
-          const int64_t q0 = b >> 2;
-          c.prim = prim_base + q0;
-          c.sec = sec_base + q0;
-          c.nq = (uint32_t)(((e + 3) >> 2) - q0);
-          c.head = (uint32_t)(b - 4 * q0);
-          c.tail = (uint32_t)(e - 4 * q0);
-          if (APP == FW_APP_METAPATH) c.want = a.schema[k % a.schema_len];
-          c.from = 0u;
-          const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, (uint32_t)k, qlo, qhi, lane, ring, ring_ptr, &s_task);
-          if (rel == 0xFFFFFFFFu) break;  // include/walker.cuh:1373-1374 (or a failed wait)
-          const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
-          if (nxt < 0 || (int64_t)nxt >= a.V) { status |= FW_STATUS_BAD_NEIGHBOR; break; }
-          if (lane == 0) row_out[k + 1] = nxt;  // include/walker.cuh:1380-1381
-          my_scanned += (unsigned long long)(e - b);
-          c.prev = cur; c.prow = a.adj + b; c.plen = (uint32_t)(e - b);  // include/gpu_task.cuh:70-77
-          cur = nxt;
-          ++k;
-          if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
-            const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(k - 1) | (fw::kPurposeStop << 28),
-                                                    qlo, qhi, a.rk);
-            if (r.x < a.tp_thresh) break;
-          }
+    // ---- hand queries to the empty slots ----
+    const uint32_t empty = __ballot_sync(0xFFFFFFFFu, slot_lane && st == 0u);
+    if (empty != 0u && !exhausted) {
+      if (res_next >= res_end) {
+        long long first = 0;
+        if (lane == 0) first = (long long)atomicAdd(a.scratch + kSlotCounter, (unsigned long long)kClaim);
+        first = __shfl_sync(0xFFFFFFFFu, first, 0);
+        if (first >= a.n) {
+          exhausted = true;
+        } else {
+          res_next = first;
+          res_end = first + kClaim < a.n ? first + kClaim : a.n;
         }
       }
-      for (int z = k + 1 + (int)lane; z <= a.d; z += 32) row_out[z] = -1;
-      my_steps += (unsigned long long)k;
-      if (lane == 0) {
-        if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
-        else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+      if (!exhausted) {
+        const long long mine = res_next + (long long)__popc(empty & ((1u << lane) - 1u));
+        if (slot_lane && st == 0u && mine < res_end) {
+          qi = mine;
+          const uint64_t qid = a.qid_base + (uint64_t)qi * a.qid_stride;
+          qlo = (uint32_t)qid;
+          qhi = (uint32_t)(qid >> 32);
+          cur = __ldg(a.starts + qi);
+          a.result[qi * D] = cur;
+          k = 0; prev = -1; pb = 0; plen = 0;
+          st = a.d > 0 ? 1u : 2u;
+          if (cur < 0 || (int64_t)cur >= a.V) { status |= FW_STATUS_BAD_START; st = 2u; }
+        }
+        res_next += (long long)__popc(empty);
+        if (res_next > res_end) res_next = res_end;
       }
     }
+    if (__ballot_sync(0xFFFFFFFFu, st != 0u) == 0u) {
+      if (exhausted) break;
+      continue;
+    }
+    // ---- row bounds of every walking slot ----
+    if (st == 1u) {
+      const OffT b = __ldg(xadj + cur), e = __ldg(xadj + cur + 1);
+      rb = b;
+      rlen = e > b ? (uint32_t)(e - b) : 0u;
+      if (rlen == 0u) st = 2u;  // dead end
+    }
+    // ---- the weighted pick: the whole warp on one slot's row at a time ----
+    for (uint32_t m = __ballot_sync(0xFFFFFFFFu, st == 1u); m != 0u; m &= m - 1u) {
+      const int s = __ffs((int)m) - 1;
+      const int64_t b = (int64_t)__shfl_sync(0xFFFFFFFFu, rb, s);
+      const uint32_t len = __shfl_sync(0xFFFFFFFFu, rlen, s);
+      const uint32_t ks = (uint32_t)__shfl_sync(0xFFFFFFFFu, k, s);
+      const uint32_t ql = __shfl_sync(0xFFFFFFFFu, qlo, s), qh = __shfl_sync(0xFFFFFFFFu, qhi, s);
+      const int64_t q0 = b >> 2;
+      StepCtx c;
+      c.prim = prim_base + q0;
+      c.sec = sec_base + q0;
+      c.head = (uint32_t)(b - 4 * q0);
+      c.tail = c.head + len;
+      c.nq = (c.tail + 3u) >> 2;
+      c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0;
+      if (APP == FW_APP_NODE2VEC) {
+        c.prev = __shfl_sync(0xFFFFFFFFu, prev, s);
+        c.prow = a.adj + (int64_t)__shfl_sync(0xFFFFFFFFu, pb, s);
+        c.plen = __shfl_sync(0xFFFFFFFFu, plen, s);
+      }
+      if (APP == FW_APP_METAPATH) c.want = a.schema[ks % (uint32_t)a.schema_len];
+      c.from = 0u;
+      c.flags = &s_flags[APP == FW_APP_NODE2VEC ? warp : 0][0];
+      FW_PROF(const long long ts0 = clock64();)
+      const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, ks, ql, qh, lane, ring, ring_ptr, &s_task);
+      FW_PROF(const long long ts1 = clock64(); const int cls = c.nq <= 32u ? 0 : c.nq <= 2u * fw::kQuadsPerSub ? 1 : 2;
+              prof_t[cls] += (unsigned long long)(ts1 - ts0); prof_n[cls] += 1ull;
+              if (cls == 2) prof_sub += (c.nq + fw::kQuadsPerSub - 1) / fw::kQuadsPerSub;)
+      if (ring.failed) break;
+      if ((int)lane == s) my_rel = rel;
+    }
+    if (ring.failed) break;
+    // ---- every walking slot takes its step ----
+    if (st == 1u) {
+      if (my_rel == kNone) {
+        st = 2u;  // no edge with a positive bias: include/walker.cuh:1373-1374
+      } else {
+        const int32_t nxt = __ldg(a.adj + (4 * ((int64_t)rb >> 2) + (int64_t)my_rel));
+        if (nxt < 0 || (int64_t)nxt >= a.V) {
+          status |= FW_STATUS_BAD_NEIGHBOR;
+          st = 2u;
+        } else {
+          a.result[qi * D + k + 1] = nxt;  // include/walker.cuh:1380-1381
+          my_scanned += (unsigned long long)rlen;
+          prev = cur; pb = rb; plen = rlen;  // include/gpu_task.cuh:70-77
+          cur = nxt;
+          ++k;
+          bool stop = k >= a.d;
+          if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
+            const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(k - 1) | (fw::kPurposeStop << 28), qlo, qhi, a.rk);
+            stop = stop || r.x < a.tp_thresh;
+          }
+          if (stop) st = 2u;
+        }
+      }
+    }
+    // ---- close the walks that ended: -1 padding by the whole warp, counters by the slot's lane ----
+    for (uint32_t m = __ballot_sync(0xFFFFFFFFu, st == 2u); m != 0u; m &= m - 1u) {
+      const int s = __ffs((int)m) - 1;
+      const long long qs = __shfl_sync(0xFFFFFFFFu, qi, s);
+      const int ks = __shfl_sync(0xFFFFFFFFu, k, s);
+      int32_t* __restrict__ row_out = a.result + qs * D;
+      for (int z = ks + 1 + (int)lane; z <= a.d; z += 32) row_out[z] = -1;
+    }
+    if (st == 2u) {
+      my_steps += (unsigned long long)k;
+      if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
+      else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+      st = 0u;
+    }
   }
+  FW_PROF(if (lane == 0) {
+    const unsigned long long life = (unsigned long long)(clock64() - prof_begin);
+    for (int i = 0; i < 3; ++i) { atomicAdd(&g_prof[i], prof_t[i]); atomicAdd(&g_prof[3 + i], prof_n[i]); }
+    atomicAdd(&g_prof[6], prof_sub);
+    atomicAdd(&g_prof[8], life - prof_t[0] - prof_t[1] - prof_t[2]);
+    atomicAdd(&g_prof[9], life);
+  })
   // Out of queries: lend a hand to the rows the CTA's other warps post until all of them are done.
   if (MODE == kModeStripShared) {
     if (lane == 0) atomicSub(&s_task.walking, 1u);
@@ -1179,6 +1497,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
 #pragma unroll
     for (int t = 0; t < kStages; ++t) mbar_wait(ring.bar + 8u * t, (ring.parity >> t) & 1u);
   }
+  // the slots' counters live in lanes 0 .. slots - 1
+#pragma unroll
+  for (int off = 1; off < slots_of<APP>(); off <<= 1) {
+    my_steps += __shfl_xor_sync(0xFFFFFFFFu, my_steps, off);
+    my_scanned += __shfl_xor_sync(0xFFFFFFFFu, my_scanned, off);
+  }
+  status = __reduce_or_sync(0xFFFFFFFFu, status);
   if (lane == 0) {
     if (my_steps) atomicAdd(a.scratch + kSlotSteps, my_steps);
     if (my_scanned) atomicAdd(a.scratch + kSlotScanned, my_scanned);
@@ -1219,7 +1544,8 @@ inline KernelFn pick_kernel(int app, int mode, bool clean, bool shared, int xadj
 // Dynamic shared memory of one CTA: the warps' rings, then the histogram.
 inline size_t kernel_smem_bytes(int app, int mode, int d, bool hist_in_smem) {
   size_t ring = 0;
-  if (mode != FW_GROUP_EDGE) ring = (size_t)kWarpsPerCta * kStages * kSubBytes;
+  if (mode != FW_GROUP_EDGE)
+    ring = (size_t)kWarpsPerCta * (app == FW_APP_NODE2VEC ? ring_bytes<FW_APP_NODE2VEC>() : ring_bytes<FW_APP_DEEPWALK>());
   return ring + (hist_in_smem ? (size_t)(d + 1) * 4 : 0);
 }
 

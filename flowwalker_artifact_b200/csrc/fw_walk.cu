@@ -183,7 +183,7 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   FW_CUDA(cudaMemsetAsync(d_scratch, 0, words * 8, st));
   FW_CUDA(cudaEventRecord(ev_begin, st));
   if (n > 0) {
-    const int64_t want = (n + (kThreads / 32) * kClaim - 1) / ((kThreads / 32) * kClaim);
+    const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
     const int grid = (int)std::min<int64_t>((int64_t)e->sms * per_sm, std::max<int64_t>(want, 1));
     void* params[] = {&a};
     FW_CUDA(cudaLaunchKernel((const void*)fn, dim3(grid), dim3(kThreads), params, smem, st));
@@ -622,7 +622,7 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
   // the array keeps the previous call's counters: everything this call reads starts at zero
   FW_CUDA(cudaMemsetAsync(scratch, 0, words * 8, st));
   if (n > 0) {
-    const int64_t want = (n + (kThreads / 32) * kClaim - 1) / ((kThreads / 32) * kClaim);
+    const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
     const int grid = (int)std::min<int64_t>((int64_t)sms * per_sm, std::max<int64_t>(want, 1));
     void* params[] = {&a};
     FW_CUDA(cudaLaunchKernel((const void*)fn, dim3(grid), dim3(kThreads), params, smem, st));
@@ -645,3 +645,17 @@ extern "C" int fw_walk_csr_noalloc(int device, int64_t V, int64_t E, const void*
     return fw::fail(FW_ERR_DEVICE, "the walk kernel gave up waiting for a staged copy; the result is incomplete");
   return FW_OK;
 }
+
+#ifdef FW_PHASE_TIMERS
+// Development aid (only in builds with -DFW_PHASE_TIMERS): reads, and optionally clears, the
+// per-phase cycle counters of the current device.
+extern "C" int fw_debug_profile(unsigned long long* out16, int reset) {
+  if (out16 && cudaMemcpyFromSymbol(out16, g_prof, sizeof(unsigned long long) * 16) != cudaSuccess)
+    return fw::fail(FW_ERR_CUDA, "cudaMemcpyFromSymbol failed");
+  if (reset) {
+    unsigned long long zero[16] = {};
+    if (cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) != cudaSuccess) return fw::fail(FW_ERR_CUDA, "cudaMemcpyToSymbol failed");
+  }
+  return FW_OK;
+}
+#endif

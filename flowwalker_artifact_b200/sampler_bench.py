@@ -33,11 +33,13 @@ def main():
     ap.add_argument("--degrees", default="16,128,1024,8192,65536")
     ap.add_argument("--d", type=int, default=40)
     ap.add_argument("--group", type=int, default=0)
+    ap.add_argument("--edges", type=int, default=1 << 26,
+                    help="edges of each graph (2^26 = 268 MB of weights: twice the L2; 2^24 stays L2-resident)")
     ap.add_argument("--work", type=float, default=0.0,
                     help="neighbours to scan per launch (default 4e11; a small value keeps instrumented ncu captures short)")
     args = ap.parse_args()
     for degree in [int(x) for x in args.degrees.split(",")]:
-        g, V = regular_graph(degree)
+        g, V = regular_graph(degree, edges=args.edges)
         eng = fw.Engine(g, 0)
         target = args.work or (4e11 if degree >= 64 else 5e10)
         n = int(min(max(target / (degree * args.d), 20000), 8e6))
@@ -48,7 +50,7 @@ def main():
         torch.cuda.synchronize()
         eng.walk_device(prm, starts.data_ptr(), n, res.data_ptr())          # warm-up
         st = eng.walk_device(prm, starts.data_ptr(), n, res.data_ptr())
-        print(json.dumps({"app": args.app, "degree": degree, "queries": n, "steps": st.steps,
+        print(json.dumps({"app": args.app, "degree": degree, "edges": args.edges, "queries": n, "steps": st.steps,
                           "kernel_ms": st.device_ms, "steps_per_s": st.steps / (st.device_ms * 1e-3),
                           "neighbours_per_s": st.scanned / (st.device_ms * 1e-3)}), flush=True)
         eng.close()
