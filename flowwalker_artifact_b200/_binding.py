@@ -77,6 +77,8 @@ def lib():
         L.fw_engine_destroy.restype = None
         L.fw_engine_device.argtypes = [vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         L.fw_engine_set_sharing.argtypes = [vp, ctypes.c_int]
+        L.fw_engine_set_hub_batching.argtypes = [vp, ctypes.c_int]
+        L.fw_engine_hubs.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(ctypes.c_uint32)]
         L.fw_walk_device.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, vp,
                                      ctypes.POINTER(WalkStats), vp]
         L.fw_walk.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, ctypes.POINTER(WalkStats), vp]
@@ -214,6 +216,17 @@ class Engine:
     def set_sharing(self, mode):
         """-1: by max degree (default), 0: never, 1: always share very long rows between warps."""
         _check(lib().fw_engine_set_sharing(self._h, mode))
+
+    def set_hub_batching(self, mode):
+        """-1: when the graph has hub vertices (default), 0: never, 1: as -1 but batching to the last
+        walker.  Walkers that meet at a hub share one sweep of its row."""
+        _check(lib().fw_engine_set_hub_batching(self._h, mode))
+
+    def hubs(self):
+        """(number of hub vertices, row length from which a vertex is a hub)."""
+        n, t = ctypes.c_int32(), ctypes.c_uint32()
+        _check(lib().fw_engine_hubs(self._h, n, t))
+        return n.value, t.value
 
     def walk(self, params, starts, want_hist=False):
         """Host buffers in, host result out (fw_walk)."""

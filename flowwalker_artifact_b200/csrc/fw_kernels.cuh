@@ -68,7 +68,29 @@ static __device__ unsigned long long g_prof[16];
 // Scratch words (uint64) in device memory.
 constexpr int kSlotSteps = 0, kSlotScanned = 1, kSlotStatus = 2, kSlotCounter = 3, kSlotHist = 4;
 
+// Hub batching (see hub_kernel): where walkers that arrive at a hub vertex are parked, and what a
+// launch that resumes parked walkers works from.  All pointers are device memory.
+struct HubArgs {
+  const int32_t* hub_ids;   // the hub vertices, ascending; a vertex is a hub iff its row has >= min_degree edges
+  int32_t n_hubs;
+  uint32_t min_degree;
+  int32_t* kstate;          // steps taken so far by every query that is parked or listed
+  const int32_t* list;      // walk kernel: queries to resume (nullptr: fresh queries 0 .. n-1)
+  const uint32_t* list_n;   // their number
+  int32_t* park_hub;        // parked walkers: hub index ...
+  int32_t* park_qi;         // ... and query
+  uint32_t* park_n;
+  uint32_t* hub_cnt;        // parked walkers per hub
+  int32_t* next_list;       // hub kernel: walkers that go on from a vertex that is not a hub
+  uint32_t* next_n;
+  const int32_t* bucket;    // hub kernel: the parked queries grouped by hub
+  const int4* items;        // (hub index, first entry in bucket, entries <= 32, unused) per batch
+  const uint32_t* items_n;
+  unsigned long long* work; // work counter of this launch
+};
+
 struct WalkArgs {
+  HubArgs hub;
   const void* xadj;
   const int32_t* adj;
   const float* weight;
@@ -1300,7 +1322,105 @@ constexpr int min_blocks() {
   return MODE == FW_GROUP_EDGE ? 2 : APP == FW_APP_NODE2VEC ? FW_N2V_MIN_BLOCKS : FW_MIN_BLOCKS;
 }
 
-template <int APP, int MODE, bool CLEAN, typename OffT>
+// The strip sampler on a row of at most 256 quads (one 4 KB stage: every row that is not a hub's)
+// that was staged ahead into stage T of the warp's ring: the copy of the next slot's row is in
+// flight while this one is reduced.  Same strips, keys and pick as sample_row_warp.
+template <int APP, bool CLEAN>
+__device__ __forceinline__ uint32_t sample_staged(const WalkArgs& a, const StepCtx& c, uint32_t step, uint32_t qlo,
+                                                  uint32_t qhi, uint32_t lane, Ring& ring, const unsigned char* ring_ptr,
+                                                  uint32_t T) {
+  const uint32_t c1 = step | (fw::kPurposeScan << 28);
+  const fw::Philox4 r = fw::philox4x32_10(lane, c1, qlo, qhi, a.rk);
+  const uint32_t ok = mbar_wait_inline(ring.bar + 8u * T, (ring.parity >> T) & 1u);
+  ring.parity ^= 1u << T;
+  if (!__all_sync(0xFFFFFFFFu, ok != 0u)) { ring.failed = true; return 0xFFFFFFFFu; }
+  const unsigned char* stage = ring_ptr + T * kHalfBytes;
+  const int4* st = reinterpret_cast<const int4*>(stage) + lane;
+  Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
+  if (c.nq <= 32u) {
+    // one quad per lane, strip = that quad; the winner's quad travels by shuffle
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (lane < c.nq) {
+      v = plain_bias<APP, CLEAN>(st[0], c.want);
+      mask_quad(v, lane, c.head, c.tail);
+    }
+    offer(best, r.x, r.w, sum4(v), lane);
+    warp_argmin(best.key, best.id);
+    if (best.id == 0xFFFFFFFFu) return best.id;
+    const int src = (int)best.id;
+    v.x = __shfl_sync(0xFFFFFFFFu, v.x, src);
+    v.y = __shfl_sync(0xFFFFFFFFu, v.y, src);
+    v.z = __shfl_sync(0xFFFFFFFFu, v.z, src);
+    v.w = __shfl_sync(0xFFFFFFFFu, v.w, src);
+    const uint32_t pick = __shfl_sync(0xFFFFFFFFu, r.w, src);
+    const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, sum4(v));
+    const float p0 = v.x, p1 = __fadd_rn(p0, v.y), p2 = __fadd_rn(p1, v.z), p3 = __fadd_rn(p2, v.w);
+    uint32_t cnt = (p0 <= thr ? 1u : 0u) + (p1 <= thr ? 1u : 0u) + (p2 <= thr ? 1u : 0u) + (p3 <= thr ? 1u : 0u);
+    if (cnt >= 4u) cnt = v.w > 0.0f ? 3u : v.z > 0.0f ? 2u : v.y > 0.0f ? 1u : 0u;
+    return 4u * (uint32_t)src + cnt;
+  }
+  // strip l = quads 32 j + l, j < 8: sub-blocks 0 and 1 of supergroup 0 (the others are empty, and
+  // adding their zeros leaves (A0+A1)+(A2+A3) = A0+A1 bit for bit).  Quads past the row, stale
+  // bytes of the stage included, are masked.
+  float S[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float4 v = plain_bias<APP, CLEAN>(st[32 * j], c.want);
+    mask_quad(v, 32u * j + lane, c.head, c.tail);
+    S[j] = sum4(v);
+  }
+  float W = sum_strip(S);
+  if (c.nq > (uint32_t)fw::kQuadsPerSub) {  // warp-uniform
+#pragma unroll
+    for (int j = 4; j < 8; ++j) {
+      float4 v = plain_bias<APP, CLEAN>(st[32 * j], c.want);
+      mask_quad(v, 32u * j + lane, c.head, c.tail);
+      S[j] = sum4(v);
+    }
+    W = __fadd_rn(W, sum_strip(S + 4));
+  }
+  offer(best, r.x, r.w, W, lane);
+  warp_argmin(best.key, best.id);
+  const uint32_t B = best.id;
+  if (B == 0xFFFFFFFFu) return B;
+  return pick_in_row<APP, CLEAN, true>(a, c, B, __shfl_sync(0xFFFFFFFFu, best.pick, (int)B),
+                                       __shfl_sync(0xFFFFFFFFu, best.W, (int)B), lane, stage);
+}
+
+// The row of c (at most 256 quads) into stage T (lane 0 only calls this).
+__device__ __forceinline__ void row_fill(const StepCtx& c, const Ring& ring, uint32_t T) {
+  mbar_expect_tx(ring.bar + 8u * T, 16u * c.nq);
+  bulk_g2s(ring.data + T * kHalfBytes, c.prim, 16u * c.nq, ring.bar + 8u * T);
+}
+
+// Index of hub vertex v in the ascending list ids[0, n) (v is known to be in it).
+__device__ __forceinline__ int32_t hub_index(const int32_t* __restrict__ ids, int32_t n, int32_t v) {
+  int32_t lo = 0, hi = n;
+  while (lo < hi) {
+    const int32_t mid = (lo + hi) >> 1;
+    if (__ldg(ids + mid) < v) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// A walker that arrived at a hub vertex `cur` after k steps waits there for the next hub launch.
+__device__ __forceinline__ void hub_park(const HubArgs& hb, long long qi, int32_t k, int32_t cur) {
+  const int32_t h = hub_index(hb.hub_ids, hb.n_hubs, cur);
+  const uint32_t pos = atomicAdd(hb.park_n, 1u);
+  hb.park_hub[pos] = h;
+  hb.park_qi[pos] = (int32_t)qi;
+  hb.kstate[qi] = k;
+  atomicAdd(hb.hub_cnt + h, 1u);
+}
+
+// HUBS: the launch is one of a series (see hub_kernel).  Walkers stop when they arrive at a hub
+// vertex and are parked for the next hub launch; the queries of the launch are either all the
+// fresh ones or the list the last hub launch left (walkers that went on from a hub to a vertex
+// that is not one).
+// The tail of the series (HUBS == kHubTail): when few walkers are left parked, batches would be
+// nearly empty; one launch then walks them to the end, every walker sweeping for itself.
+constexpr int kHubOff = 0, kHubPark = 1, kHubTail = 2;
+template <int APP, int MODE, bool CLEAN, typename OffT, int HUBS = kHubOff>
 __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()) walk_kernel(const __grid_constant__ WalkArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
@@ -1356,6 +1476,8 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
   long long res_next = 0, res_end = 0;  // queries claimed by the warp and not yet handed to a slot
   bool exhausted = false;
 
+  unsigned long long* const work = HUBS != kHubOff ? a.hub.work : a.scratch + kSlotCounter;
+  const long long n_work = (HUBS != kHubOff && a.hub.list != nullptr) ? (long long)*a.hub.list_n : (long long)a.n;
   FW_PROF(unsigned long long prof_t[3] = {0, 0, 0}, prof_n[3] = {0, 0, 0}, prof_sub = 0; const long long prof_begin = clock64();)
   while (!ring.failed) {
     // ---- hand queries to the empty slots ----
@@ -1363,27 +1485,35 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
     if (empty != 0u && !exhausted) {
       if (res_next >= res_end) {
         long long first = 0;
-        if (lane == 0) first = (long long)atomicAdd(a.scratch + kSlotCounter, (unsigned long long)kClaim);
+        if (lane == 0) first = (long long)atomicAdd(work, (unsigned long long)kClaim);
         first = __shfl_sync(0xFFFFFFFFu, first, 0);
-        if (first >= a.n) {
+        if (first >= n_work) {
           exhausted = true;
         } else {
           res_next = first;
-          res_end = first + kClaim < a.n ? first + kClaim : a.n;
+          res_end = first + kClaim < n_work ? first + kClaim : n_work;
         }
       }
       if (!exhausted) {
         const long long mine = res_next + (long long)__popc(empty & ((1u << lane) - 1u));
         if (slot_lane && st == 0u && mine < res_end) {
-          qi = mine;
+          const bool resumed = HUBS != kHubOff && a.hub.list != nullptr;
+          qi = resumed ? (long long)__ldg(a.hub.list + mine) : mine;
           const uint64_t qid = a.qid_base + (uint64_t)qi * a.qid_stride;
           qlo = (uint32_t)qid;
           qhi = (uint32_t)(qid >> 32);
-          cur = __ldg(a.starts + qi);
-          a.result[qi * D] = cur;
-          k = 0; prev = -1; pb = 0; plen = 0;
-          st = a.d > 0 ? 1u : 2u;
-          if (cur < 0 || (int64_t)cur >= a.V) { status |= FW_STATUS_BAD_START; st = 2u; }
+          prev = -1; pb = 0; plen = 0;
+          if (resumed) {  // a walker the last hub launch moved on: its state is what the table holds
+            k = a.hub.kstate[qi];
+            cur = a.result[qi * D + k];
+            st = 1u;
+          } else {
+            cur = __ldg(a.starts + qi);
+            a.result[qi * D] = cur;
+            k = 0;
+            st = a.d > 0 ? 1u : 2u;
+            if (cur < 0 || (int64_t)cur >= a.V) { status |= FW_STATUS_BAD_START; st = 2u; }
+          }
         }
         res_next += (long long)__popc(empty);
         if (res_next > res_end) res_next = res_end;
@@ -1398,9 +1528,58 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
       const OffT b = __ldg(xadj + cur), e = __ldg(xadj + cur + 1);
       rb = b;
       rlen = e > b ? (uint32_t)(e - b) : 0u;
-      if (rlen == 0u) st = 2u;  // dead end
+      if (rlen == 0u) {
+        st = 2u;  // dead end
+      } else if (HUBS == kHubPark && rlen >= a.hub.min_degree) {
+        hub_park(a.hub, qi, k, cur);  // the slot is free again; the hub launch takes the walker from here
+        st = 0u;
+      }
     }
     // ---- the weighted pick: the whole warp on one slot's row at a time ----
+    if constexpr (HUBS == kHubPark) {
+      // Every row here is shorter than a hub's: one 4 KB stage holds it.  The two stages take
+      // turns, so the next slot's row is on its way while this slot's is reduced.
+      uint32_t m = __ballot_sync(0xFFFFFFFFu, st == 1u);
+      if (m != 0u) {
+        auto slot_ctx = [&](int s, StepCtx& c, uint32_t& ks, uint32_t& ql, uint32_t& qh) {
+          const int64_t b = (int64_t)__shfl_sync(0xFFFFFFFFu, rb, s);
+          const uint32_t len = __shfl_sync(0xFFFFFFFFu, rlen, s);
+          ks = (uint32_t)__shfl_sync(0xFFFFFFFFu, k, s);
+          ql = __shfl_sync(0xFFFFFFFFu, qlo, s);
+          qh = __shfl_sync(0xFFFFFFFFu, qhi, s);
+          const int64_t q0 = b >> 2;
+          c.prim = prim_base + q0;
+          c.sec = sec_base + q0;
+          c.head = (uint32_t)(b - 4 * q0);
+          c.tail = c.head + len;
+          c.nq = (c.tail + 3u) >> 2;
+          c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = nullptr;
+        };
+        int s = __ffs((int)m) - 1;
+        m &= m - 1u;
+        StepCtx c;
+        uint32_t ks, ql, qh, T = 0u;
+        slot_ctx(s, c, ks, ql, qh);
+        if (lane == 0) row_fill(c, ring, T);
+        for (;;) {
+          int s2 = -1;
+          StepCtx c2;
+          uint32_t ks2 = 0, ql2 = 0, qh2 = 0;
+          if (m != 0u) {
+            s2 = __ffs((int)m) - 1;
+            m &= m - 1u;
+            slot_ctx(s2, c2, ks2, ql2, qh2);
+            if (lane == 0) row_fill(c2, ring, T ^ 1u);
+          }
+          const uint32_t rel = sample_staged<APP, CLEAN>(a, c, ks, ql, qh, lane, ring, ring_ptr, T);
+          if (ring.failed) break;
+          if ((int)lane == s) my_rel = rel;
+          if (s2 < 0) break;
+          s = s2; c = c2; ks = ks2; ql = ql2; qh = qh2;
+          T ^= 1u;
+        }
+      }
+    } else
     for (uint32_t m = __ballot_sync(0xFFFFFFFFu, st == 1u); m != 0u; m &= m - 1u) {
       const int s = __ffs((int)m) - 1;
       const int64_t b = (int64_t)__shfl_sync(0xFFFFFFFFu, rb, s);
@@ -1516,7 +1695,307 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
   }
 }
 
+// ---- hub launches: one sweep of a hub's row serves up to 32 walkers ----
+//
+// Most of what a walk reads are the rows of a few thousand hub vertices, and at any moment many
+// walkers sit on the same hub.  The strip totals W(s,l) of a row do not depend on the walker
+// (DeepWalk, PPR), only the random words do, so walkers that wait at the same hub are served
+// together: the row is swept once by a warp, and after every three supergroups lane q, which
+// stands for walker q of the batch, forms walker q's keys for the 96 strips just summed from its
+// own Philox blocks (the totals travel by shuffle).  What a walker costs on a hub row drops from
+// the row's bytes to one Philox block per three strips, and the bytes are read once per batch.
+// The walks are the same as without batching: key, strip id and pick word of every walker are
+// what its own sweep would have formed, and the smallest (key, id) wins either way.
+//
+// A walk call becomes a series of launches on one stream: the walk kernel runs every walker until
+// it arrives at a hub and parks it there (hub_park); hub_plan_kernel and hub_scatter_kernel
+// group the parked walkers by hub into batches of up to 32; hub_kernel serves the batches and
+// parks the walkers whose next vertex is a hub again, lists the others for the walk kernel; and
+// so on until nobody is parked.
+
+// Exact test of one strip for one walker, behind the same lower-bound filter as offer_filtered;
+// ties go to the lower strip id (the strips of a walker do not arrive in id order here).
+__device__ __forceinline__ void offer_lex(Best& b, uint32_t x, uint32_t pick_word, float W, uint32_t id) {
+  if (!(W > 0.0f)) return;
+  const int g = __clz((int)x);
+  const float lower = g ? (float)g : __fmul_rn((float)(x << 1), 0.72f * 0x1p-32f);
+  if (lower > __fmul_rn(__fmul_rn(__uint_as_float(b.key), W), 1.000001f)) return;  // NaN bound (nothing yet): passes
+  const uint32_t bits = __float_as_uint(__fdiv_rn(fw::exp_key(x), W));
+  if (bits < b.key || (bits == b.key && id < b.id)) { b.key = bits; b.id = id; b.pick = pick_word; b.W = W; }
+}
+
+// pick_in_row by one lane for its own walker: the strip's quads one after the other from global
+// memory (the row was just swept: they come from L2).
+template <int APP, bool CLEAN>
+__device__ __forceinline__ uint32_t pick_lane(const StepCtx& c, uint32_t B, uint32_t pick, float W) {
+  const uint32_t sB = B >> 5, lB = B & 31u;
+  const float thr = __fmul_rn((float)(pick >> 8) * 0x1p-24f, W);
+  const uint32_t last_blk = (c.nq - 1u) >> 5;
+  const uint32_t blk0 = 16u * sB;
+  const uint32_t nblk = min(16u, last_blk - blk0 + 1u);
+  float acc = 0.0f;
+  uint32_t cnt = 0, j = 0, last_pos = 0;
+#pragma unroll 1
+  for (; j < nblk; ++j) {
+    const uint32_t q = 32u * (blk0 + j) + lB;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (q < c.nq) {
+      v = plain_bias<APP, CLEAN>(__ldg(c.prim + q), c.want);
+      mask_quad(v, q, c.head, c.tail);
+    }
+    if (v.x > 0.0f) last_pos = 4u * j;
+    if (v.y > 0.0f) last_pos = 4u * j + 1u;
+    if (v.z > 0.0f) last_pos = 4u * j + 2u;
+    if (v.w > 0.0f) last_pos = 4u * j + 3u;
+    const float p0 = __fadd_rn(acc, v.x), p1 = __fadd_rn(p0, v.y), p2 = __fadd_rn(p1, v.z);
+    acc = __fadd_rn(p2, v.w);
+    if (acc <= thr) { cnt += 4u; continue; }
+    cnt += (p0 <= thr ? 1u : 0u) + (p1 <= thr ? 1u : 0u) + (p2 <= thr ? 1u : 0u);
+    break;
+  }
+  if (j == nblk) cnt = last_pos;  // rounding pushed u * W past the sequential total: the last positive edge
+  return 4u * (32u * (blk0 + (cnt >> 2)) + lB) + (cnt & 3u);
+}
+
+template <int APP, bool CLEAN, typename OffT>
+__global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __grid_constant__ WalkArgs a) {
+  static_assert(APP == FW_APP_DEEPWALK || APP == FW_APP_PPR, "strip totals must not depend on the walker");
+  extern __shared__ __align__(128) unsigned char s_dyn[];
+  __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][2];
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  constexpr uint32_t kRingPerWarp = ring_bytes<APP>();
+  uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
+  const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
+  Ring ring;
+  ring.data = smem_addr(ring_ptr);
+  ring.bar = smem_addr(&s_bar[warp][0]);
+  ring.parity = 0u;
+  ring.failed = false;
+  if (lane == 0) {
+    mbar_init(ring.bar, 1u);
+    mbar_init(ring.bar + 8u, 1u);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (a.hist_in_smem)
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x) s_hist[z] = 0u;
+  __syncthreads();
+
+  const OffT* __restrict__ xadj = static_cast<const OffT*>(a.xadj);
+  const int64_t D = (int64_t)a.d + 1;
+  const int4* const prim_base = reinterpret_cast<const int4*>(a.weight);
+  const int4* const lane_ptr = reinterpret_cast<const int4*>(ring_ptr) + lane;
+  const uint32_t n_items = *a.hub.items_n;
+  unsigned long long my_steps = 0, my_scanned = 0;
+  uint32_t status = 0;
+
+  while (!ring.failed) {
+    unsigned long long item = 0;
+    if (lane == 0) item = atomicAdd(a.hub.work, 1ull);
+    item = __shfl_sync(0xFFFFFFFFu, item, 0);
+    if (item >= (unsigned long long)n_items) break;
+    const int4 it = __ldg(a.hub.items + item);  // hub index, first entry, entries
+    const int32_t v = __ldg(a.hub.hub_ids + it.x);
+    const int64_t b = (int64_t)__ldg(xadj + v);
+    const uint32_t len = (uint32_t)((int64_t)__ldg(xadj + v + 1) - b);
+    const int64_t q0 = b >> 2;
+    StepCtx c;
+    c.prim = prim_base + q0;
+    c.sec = nullptr;
+    c.head = (uint32_t)(b - 4 * q0);
+    c.tail = c.head + len;
+    c.nq = (c.tail + 3u) >> 2;
+    c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = nullptr;
+    // the walker this lane stands for
+    const bool have = lane < (uint32_t)it.z;
+    const long long qi = have ? (long long)__ldg(a.hub.bucket + it.y + lane) : 0;
+    int32_t k = have ? a.hub.kstate[qi] : 0;
+    const uint64_t qid = a.qid_base + (uint64_t)qi * a.qid_stride;
+    const uint32_t qlo = (uint32_t)qid, qhi = (uint32_t)(qid >> 32);
+    const uint32_t c1 = (uint32_t)k | (fw::kPurposeScan << 28);
+    Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
+
+    // ---- one sweep of the row; the walkers' keys after every third supergroup ----
+    const uint32_t n_half = (c.nq + kHalfQuads - 1u) / kHalfQuads;
+    const uint32_t end_super = ((n_half + 1u) >> 1) - 1u;
+    if (lane == 0) {
+      half_fill(c, ring, 0u);
+      if (n_half > 1u) half_fill(c, ring, 1u);
+    }
+    float W0 = 0.0f, W1 = 0.0f, W2 = 0.0f;
+    uint32_t g = 0, m = 0;
+#pragma unroll 1
+    for (uint32_t sg = 0;; ++sg) {
+      const bool last = sg == end_super;
+      float W;
+      bool ok;
+      if (sg == 0u || last) ok = super_turn<APP, CLEAN, true>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
+      else ok = super_turn<APP, CLEAN, false>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
+      if (!ok) { ring.failed = true; break; }
+      if (m == 0u) W0 = W; else if (m == 1u) W1 = W; else W2 = W;
+      if (m == 2u || last) {
+        // lane q: walker q's keys for strips (3g .. 3g+2, l), l = 0 .. 31
+#pragma unroll 1
+        for (int l = 0; l < 32; ++l) {
+          const float w0 = __shfl_sync(0xFFFFFFFFu, W0, l), w1 = __shfl_sync(0xFFFFFFFFu, W1, l);
+          const float w2 = __shfl_sync(0xFFFFFFFFu, W2, l);
+          const fw::Philox4 r = fw::philox4x32_10(g * 32u + (uint32_t)l, c1, qlo, qhi, a.rk);
+          offer_lex(best, r.x, r.w, w0, (3u * g) * 32u + (uint32_t)l);
+          offer_lex(best, r.y, r.w, w1, (3u * g + 1u) * 32u + (uint32_t)l);
+          offer_lex(best, r.z, r.w, w2, (3u * g + 2u) * 32u + (uint32_t)l);
+        }
+        W0 = 0.0f; W1 = 0.0f; W2 = 0.0f;
+        m = 0u;
+        ++g;
+      } else {
+        ++m;
+      }
+      if (last) break;
+    }
+    if (ring.failed) break;
+
+    // ---- every walker takes its step ----
+    bool fin = false;
+    if (have) {
+      if (best.id == 0xFFFFFFFFu) {
+        fin = true;  // no edge with a positive bias
+      } else {
+        const uint32_t rel = pick_lane<APP, CLEAN>(c, best.id, best.pick, best.W);
+        const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
+        if (nxt < 0 || (int64_t)nxt >= a.V) {
+          status |= FW_STATUS_BAD_NEIGHBOR;
+          fin = true;
+        } else {
+          a.result[qi * D + k + 1] = nxt;
+          my_scanned += (unsigned long long)len;
+          ++k;
+          bool stop = k >= a.d;
+          if (APP == FW_APP_PPR) {
+            const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(k - 1) | (fw::kPurposeStop << 28), qlo, qhi, a.rk);
+            stop = stop || r.x < a.tp_thresh;
+          }
+          if (stop) {
+            fin = true;
+          } else {
+            // where the walker goes on: parked at the next hub, or listed for the walk kernel
+            const OffT nb = __ldg(xadj + nxt), ne = __ldg(xadj + nxt + 1);
+            if (ne <= nb) {
+              fin = true;  // dead end
+            } else if ((uint64_t)(ne - nb) >= (uint64_t)a.hub.min_degree) {
+              hub_park(a.hub, qi, k, nxt);
+            } else {
+              const uint32_t pos = atomicAdd(a.hub.next_n, 1u);
+              a.hub.next_list[pos] = (int32_t)qi;
+              a.hub.kstate[qi] = k;
+            }
+          }
+        }
+      }
+    }
+    // ---- close the walks that ended ----
+    for (uint32_t mm = __ballot_sync(0xFFFFFFFFu, fin); mm != 0u; mm &= mm - 1u) {
+      const int s = __ffs((int)mm) - 1;
+      const long long qs = __shfl_sync(0xFFFFFFFFu, qi, s);
+      const int ks = __shfl_sync(0xFFFFFFFFu, k, s);
+      int32_t* __restrict__ row_out = a.result + qs * D;
+      for (int z = ks + 1 + (int)lane; z <= a.d; z += 32) row_out[z] = -1;
+    }
+    if (fin) {
+      my_steps += (unsigned long long)k;
+      if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
+      else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+    }
+  }
+  if (ring.failed) {
+    status |= FW_STATUS_WAIT_TIMEOUT;
+    mbar_wait(ring.bar, ring.parity & 1u);
+    mbar_wait(ring.bar + 8u, (ring.parity >> 1) & 1u);
+  }
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    my_steps += __shfl_xor_sync(0xFFFFFFFFu, my_steps, off);
+    my_scanned += __shfl_xor_sync(0xFFFFFFFFu, my_scanned, off);
+  }
+  status = __reduce_or_sync(0xFFFFFFFFu, status);
+  if (lane == 0) {
+    if (my_steps) atomicAdd(a.scratch + kSlotSteps, my_steps);
+    if (my_scanned) atomicAdd(a.scratch + kSlotScanned, my_scanned);
+    if (status) atomicOr(a.scratch + kSlotStatus, (unsigned long long)status);
+  }
+  if (a.hist_in_smem) {
+    __syncthreads();
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x)
+      if (s_hist[z]) atomicAdd(a.scratch + kSlotHist + z, (unsigned long long)s_hist[z]);
+  }
+}
+
+// Groups the parked walkers by hub: exclusive scan of the per-hub counts into `base`, one batch item
+// per 32 walkers of a hub, the counts and the scatter cursors back to zero.  One CTA of kPlanThreads.
+constexpr int kPlanThreads = 1024;
+__global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, uint32_t* base, uint32_t* fill, int4* items,
+                                                                uint32_t* items_n, int n_hubs) {
+  __shared__ uint32_t s_cnt[kPlanThreads], s_bat[kPlanThreads];
+  const int t = threadIdx.x;
+  const int per = (n_hubs + kPlanThreads - 1) / kPlanThreads;
+  const int h0 = min(t * per, n_hubs), h1 = min(h0 + per, n_hubs);
+  uint32_t my_cnt = 0, my_bat = 0;
+  for (int h = h0; h < h1; ++h) {
+    my_cnt += cnt[h];
+    my_bat += (cnt[h] + 31u) >> 5;
+  }
+  s_cnt[t] = my_cnt;
+  s_bat[t] = my_bat;
+  __syncthreads();
+  for (int off = 1; off < kPlanThreads; off <<= 1) {  // inclusive scan of both
+    const uint32_t x = t >= off ? s_cnt[t - off] : 0u, y = t >= off ? s_bat[t - off] : 0u;
+    __syncthreads();
+    s_cnt[t] += x;
+    s_bat[t] += y;
+    __syncthreads();
+  }
+  uint32_t at = s_cnt[t] - my_cnt, ib = s_bat[t] - my_bat;
+  for (int h = h0; h < h1; ++h) {
+    const uint32_t n = cnt[h];
+    base[h] = at;
+    for (uint32_t off = 0; off < n; off += 32u) items[ib++] = make_int4(h, (int)(at + off), (int)min(32u, n - off), 0);
+    at += n;
+    cnt[h] = 0u;
+    fill[h] = 0u;
+  }
+  if (t == kPlanThreads - 1) *items_n = s_bat[t];
+}
+
+__global__ void hub_scatter_kernel(const int32_t* __restrict__ park_hub, const int32_t* __restrict__ park_qi,
+                                   const uint32_t* __restrict__ park_n, const uint32_t* __restrict__ base, uint32_t* fill,
+                                   int32_t* __restrict__ bucket) {
+  const uint32_t n = *park_n;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int32_t h = park_hub[i];
+    bucket[base[h] + atomicAdd(fill + h, 1u)] = park_qi[i];
+  }
+}
+
 using KernelFn = void (*)(const WalkArgs);
+
+// The kernels of a hub-batched call: the walk kernel that parks walkers at hubs, and the hub kernel.
+template <int APP, int HUBS>
+inline KernelFn pick_hub_walk(bool clean, int xadj_bits) {
+  if (xadj_bits == 64)
+    return clean ? (KernelFn)walk_kernel<APP, FW_GROUP_STRIP, true, int64_t, HUBS> : (KernelFn)walk_kernel<APP, FW_GROUP_STRIP, false, int64_t, HUBS>;
+  return clean ? (KernelFn)walk_kernel<APP, FW_GROUP_STRIP, true, uint32_t, HUBS> : (KernelFn)walk_kernel<APP, FW_GROUP_STRIP, false, uint32_t, HUBS>;
+}
+template <int APP>
+inline KernelFn pick_hub_serve(bool clean, int xadj_bits) {
+  if (xadj_bits == 64) return clean ? (KernelFn)hub_kernel<APP, true, int64_t> : (KernelFn)hub_kernel<APP, false, int64_t>;
+  return clean ? (KernelFn)hub_kernel<APP, true, uint32_t> : (KernelFn)hub_kernel<APP, false, uint32_t>;
+}
+// which: 0 the walk kernel that parks at hubs, 1 the hub kernel, 2 the walk kernel of the tail
+inline KernelFn pick_hub_kernel(int app, int which, bool clean, int xadj_bits) {
+  if (app == FW_APP_PPR)
+    return which == 1 ? pick_hub_serve<FW_APP_PPR>(clean, xadj_bits)
+         : which == 2 ? pick_hub_walk<FW_APP_PPR, kHubTail>(clean, xadj_bits) : pick_hub_walk<FW_APP_PPR, kHubPark>(clean, xadj_bits);
+  return which == 1 ? pick_hub_serve<FW_APP_DEEPWALK>(clean, xadj_bits)
+       : which == 2 ? pick_hub_walk<FW_APP_DEEPWALK, kHubTail>(clean, xadj_bits) : pick_hub_walk<FW_APP_DEEPWALK, kHubPark>(clean, xadj_bits);
+}
 
 template <int APP, int MODE, bool CLEAN>
 inline KernelFn pick_off(int xadj_bits) {

@@ -16,9 +16,15 @@
 // reproduces every walk bit for bit.
 #include <cuda_runtime.h>
 
+#include <stdio.h>
+#include <string.h>
+
 #include <algorithm>
+#include <chrono>
+#include <functional>
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "fw_internal.h"
 #include "fw_kernels.cuh"
@@ -29,6 +35,23 @@ using namespace fwk;
 // Graphs with a row of at least this many edges run the kernel variant whose warps share very
 // long rows (a single warp on a row of 10^6 edges is what the tail of a launch consists of).
 static constexpr int64_t kSharingAutoDegree = 262144;
+
+// Hub batching: vertices of at least this many neighbours are hubs (about the reference's limit
+// between its warp and its block sampler, 1,024: include/walker.cuh:29).
+static constexpr int64_t kHubMinDegree = 1016;  // a row below it is at most 256 quads (4 KB) however it is aligned
+static constexpr int64_t kHubMax = (int64_t)1 << 22;
+static constexpr int64_t kHubTailMin = 2048;   // parked walkers below which a call goes to its tail launch ...
+static constexpr int64_t kHubTailShare = 64;   // ... or below this share of the call's queries
+
+// Device control words of one round of a hub-batched call.
+struct HubCtl {
+  unsigned long long work_walk;  // work counter of the round's walk kernel
+  unsigned long long work_hub;   // ... of its hub kernel
+  uint32_t park_n;               // walkers parked for this round's hub kernel
+  uint32_t list_n;               // walkers listed for this round's walk kernel
+  uint32_t items_n;              // batches of this round's hub kernel
+  uint32_t pad;
+};
 
 
 // ---------------------------------------------------------------------------
@@ -53,6 +76,23 @@ struct fw_engine {
   size_t scratch_words = 0;
   cudaStream_t stream = nullptr, stream2 = nullptr;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // hub batching: the hub vertices and the buffers of a hub-batched call (grown on demand)
+  int hub_mode = -1;           // -1: when the graph has hubs, 0: never, 1: as -1 without the tail launch
+  int32_t n_hubs = 0;
+  uint32_t hub_min_degree = 0;
+  int32_t* d_hub_ids = nullptr;
+  uint32_t* d_hub_cnt = nullptr;   // [2][n_hubs] parked walkers per hub, this round and the next
+  uint32_t* d_hub_base = nullptr;  // [n_hubs]
+  uint32_t* d_hub_fill = nullptr;  // [n_hubs]
+  size_t hub_cap = 0;              // queries the buffers below are sized for
+  int32_t* d_kstate = nullptr;
+  int32_t* d_list = nullptr;
+  int32_t* d_park_hub[2] = {nullptr, nullptr};
+  int32_t* d_park_qi[2] = {nullptr, nullptr};
+  int32_t* d_bucket = nullptr;
+  int4* d_items = nullptr;
+  unsigned char* d_ctl = nullptr;  // two HubCtl blocks
+  uint32_t* h_ctl = nullptr;       // pinned word the parked count travels to
   // staging for the host-buffer entry points (grown on demand)
   int32_t* d_starts[2] = {nullptr, nullptr};
   int32_t* d_result[2] = {nullptr, nullptr};
@@ -154,10 +194,125 @@ int prepare_kernel(KernelFn fn, size_t smem, int* per_sm) {
 }
 
 // Enqueues: scratch reset, kernel between ev[0] and ev[1], scratch read-back.
+// Buffers of a hub-batched call for n queries.
+int ensure_hub_buffers(fw_engine* e, size_t n) {
+  if (n <= e->hub_cap) return FW_OK;
+  cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
+  for (int i = 0; i < 2; ++i) { cudaFree(e->d_park_hub[i]); cudaFree(e->d_park_qi[i]); }
+  e->d_kstate = e->d_list = e->d_bucket = nullptr;
+  e->d_items = nullptr;
+  e->d_park_hub[0] = e->d_park_hub[1] = e->d_park_qi[0] = e->d_park_qi[1] = nullptr;
+  e->hub_cap = 0;
+  const size_t cap = std::max<size_t>(n, 1024);
+  FW_CUDA(cudaMalloc(&e->d_kstate, cap * 4));
+  FW_CUDA(cudaMalloc(&e->d_list, cap * 4));
+  FW_CUDA(cudaMalloc(&e->d_bucket, cap * 4));
+  for (int i = 0; i < 2; ++i) {
+    FW_CUDA(cudaMalloc(&e->d_park_hub[i], cap * 4));
+    FW_CUDA(cudaMalloc(&e->d_park_qi[i], cap * 4));
+  }
+  FW_CUDA(cudaMalloc(&e->d_items, (cap / 32 + (size_t)e->n_hubs + 1) * sizeof(int4)));
+  e->hub_cap = cap;
+  return FW_OK;
+}
+
+// The launches of a hub-batched call (see hub_kernel): the walk kernel on the fresh queries, then
+// rounds of plan, scatter, hub kernel, walk kernel while walkers are parked at hubs.  Every round
+// ends with the host reading the number of parked walkers, so this returns with the walk done.
+int run_hub_batched(fw_engine* e, const fw_walk_params* p, WalkArgs a, int64_t n, cudaStream_t st, size_t smem,
+                    int* launches) {
+  int rc = ensure_hub_buffers(e, (size_t)n);
+  if (rc) return rc;
+  KernelFn walk_fn = pick_hub_kernel(p->app, 0, e->clean_weights, e->xadj_bits);
+  KernelFn hub_fn = pick_hub_kernel(p->app, 1, e->clean_weights, e->xadj_bits);
+  KernelFn tail_fn = pick_hub_kernel(p->app, 2, e->clean_weights, e->xadj_bits);
+  int walk_per_sm = 0, hub_per_sm = 0, tail_per_sm = 0;
+  rc = prepare_kernel(walk_fn, smem, &walk_per_sm);
+  if (!rc) rc = prepare_kernel(hub_fn, smem, &hub_per_sm);
+  if (!rc) rc = prepare_kernel(tail_fn, smem, &tail_per_sm);
+  if (rc) return rc;
+  // Below this many parked walkers the batches are mostly empty and a round costs more than it
+  // serves: the walkers left are then walked to the end by one launch, each sweeping for itself.
+  const uint32_t tail_limit = e->hub_mode == 1 ? 0u : (uint32_t)std::max<int64_t>(kHubTailMin, n / kHubTailShare);
+  HubCtl* ctl = reinterpret_cast<HubCtl*>(e->d_ctl);
+  FW_CUDA(cudaMemsetAsync(e->d_ctl, 0, 2 * sizeof(HubCtl), st));
+  FW_CUDA(cudaMemsetAsync(e->d_hub_cnt, 0, (size_t)e->n_hubs * 8, st));
+  a.hub.hub_ids = e->d_hub_ids; a.hub.n_hubs = e->n_hubs; a.hub.min_degree = e->hub_min_degree;
+  a.hub.kstate = e->d_kstate;
+  a.hub.next_list = e->d_list; a.hub.bucket = e->d_bucket; a.hub.items = e->d_items;
+  auto parks_into = [&](int set) {
+    a.hub.park_hub = e->d_park_hub[set]; a.hub.park_qi = e->d_park_qi[set];
+    a.hub.park_n = &ctl[set].park_n; a.hub.hub_cnt = e->d_hub_cnt + (size_t)set * (size_t)e->n_hubs;
+  };
+  void* params[] = {&a};
+  const int full_walk = e->sms * walk_per_sm, full_hub = e->sms * hub_per_sm;
+  // the fresh queries
+  int cur = 0;
+  parks_into(cur);
+  a.hub.list = nullptr; a.hub.list_n = nullptr; a.hub.work = &ctl[cur].work_walk;
+  {
+    const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
+    const int grid = (int)std::min<int64_t>(full_walk, std::max<int64_t>(want, 1));
+    FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(grid), dim3(kThreads), params, smem, st));
+    ++*launches;
+  }
+  const bool trace = getenv("FW_HUB_TRACE") != nullptr;  // development aid: the rounds on stderr
+  const auto t_trace = std::chrono::steady_clock::now();
+  // every round moves each parked walker at least one step on: d + 1 rounds are the most there can be
+  for (int64_t round = 0;; ++round) {
+    FW_CUDA(cudaMemcpyAsync(e->h_ctl, &ctl[cur].park_n, 4, cudaMemcpyDeviceToHost, st));
+    FW_CUDA(cudaStreamSynchronize(st));
+    const uint32_t parked = e->h_ctl[0];
+    if (trace) {
+      const double now = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_trace).count();
+      fprintf(stderr, "hub round %lld: %u parked, %.0f us since the call began\n", (long long)round, parked, now);
+    }
+    if (parked == 0) break;
+    if (parked < tail_limit) {
+      a.hub.list = e->d_park_qi[cur]; a.hub.list_n = &ctl[cur].park_n; a.hub.work = &ctl[cur].work_hub;
+      const int tgrid = (int)std::min<int64_t>((int64_t)e->sms * tail_per_sm, std::max<int64_t>(((int64_t)parked + 31) / 32, 1));
+      FW_CUDA(cudaLaunchKernel((const void*)tail_fn, dim3(tgrid), dim3(kThreads), params, smem, st));
+      ++*launches;
+      // the engine's hub buffers serve one call at a time: the next one (a batch on the other
+      // stream) may start only when this launch is through with them
+      FW_CUDA(cudaStreamSynchronize(st));
+      break;
+    }
+    if (round > (int64_t)p->d + 1) return fw::fail(FW_ERR_DEVICE, "hub batching did not come to an end (internal error)");
+    const int nxt = cur ^ 1;
+    FW_CUDA(cudaMemsetAsync(&ctl[nxt], 0, sizeof(HubCtl), st));
+    hub_plan_kernel<<<1, kPlanThreads, 0, st>>>(e->d_hub_cnt + (size_t)cur * (size_t)e->n_hubs, e->d_hub_base, e->d_hub_fill,
+                                                e->d_items, &ctl[cur].items_n, e->n_hubs);
+    const int sgrid = (int)std::min<int64_t>(((int64_t)parked + 255) / 256, (int64_t)e->sms * 8);
+    hub_scatter_kernel<<<sgrid, 256, 0, st>>>(e->d_park_hub[cur], e->d_park_qi[cur], &ctl[cur].park_n, e->d_hub_base,
+                                              e->d_hub_fill, e->d_bucket);
+    FW_CUDA(cudaGetLastError());
+    // hub kernel: serves this round's batches, parks and lists for the next
+    parks_into(nxt);
+    a.hub.items_n = &ctl[cur].items_n; a.hub.work = &ctl[cur].work_hub; a.hub.next_n = &ctl[nxt].list_n;
+    a.hub.list = nullptr; a.hub.list_n = nullptr;
+    const int64_t max_items = (int64_t)parked / 32 + e->n_hubs;
+    const int hgrid = (int)std::min<int64_t>(full_hub, std::max<int64_t>((max_items + 7) / 8, 1));
+    FW_CUDA(cudaLaunchKernel((const void*)hub_fn, dim3(hgrid), dim3(kThreads), params, smem, st));
+    // walk kernel: the walkers the hub kernel listed
+    a.hub.list = e->d_list; a.hub.list_n = &ctl[nxt].list_n; a.hub.work = &ctl[nxt].work_walk;
+    const int wgrid = (int)std::min<int64_t>(full_walk, std::max<int64_t>(((int64_t)parked + 31) / 32, 1));
+    FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(wgrid), dim3(kThreads), params, smem, st));
+    *launches += 4;
+    cur = nxt;
+  }
+  return FW_OK;
+}
+
+// Enqueues: scratch reset, kernel(s) between ev_begin and ev_end, scratch read-back.  *launches
+// receives the number of kernel launches.  A hub-batched call has returned from its last kernel
+// when this returns; a single-kernel call is only enqueued.
 int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_dev, int64_t n,
                  int32_t* result_dev, cudaStream_t st, cudaEvent_t ev_begin, cudaEvent_t ev_end,
-                 unsigned long long* d_scratch, unsigned long long* h_scratch) {
+                 unsigned long long* d_scratch, unsigned long long* h_scratch, int* launches) {
+  *launches = 0;
   WalkArgs a;
+  memset(&a.hub, 0, sizeof(a.hub));
   a.xadj = e->d_xadj; a.adj = e->d_adj; a.weight = e->d_weight; a.label = e->d_label;
   a.V = e->V; a.starts = starts_dev; a.n = n; a.result = result_dev; a.scratch = d_scratch;
   a.qid_base = p->query_id_base; a.qid_stride = p->query_id_stride ? p->query_id_stride : 1; a.d = p->d;
@@ -182,11 +337,19 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   const size_t words = (size_t)kSlotHist + (size_t)p->d + 1;
   FW_CUDA(cudaMemsetAsync(d_scratch, 0, words * 8, st));
   FW_CUDA(cudaEventRecord(ev_begin, st));
-  if (n > 0) {
+  // Hub batching: DeepWalk and PPR (their strip totals do not depend on the walker) with the strip
+  // sampler, on graphs that have hub vertices.  Query and vertex numbers must fit 31 bits.
+  const bool hubs = e->hub_mode != 0 && e->n_hubs > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
+                    (p->app == FW_APP_DEEPWALK || p->app == FW_APP_PPR) && n < ((int64_t)1 << 31);
+  if (n > 0 && hubs) {
+    const int hrc = run_hub_batched(e, p, a, n, st, smem, launches);
+    if (hrc) return hrc;
+  } else if (n > 0) {
     const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
     const int grid = (int)std::min<int64_t>((int64_t)e->sms * per_sm, std::max<int64_t>(want, 1));
     void* params[] = {&a};
     FW_CUDA(cudaLaunchKernel((const void*)fn, dim3(grid), dim3(kThreads), params, smem, st));
+    *launches = 1;
   }
   FW_CUDA(cudaEventRecord(ev_end, st));
   FW_CUDA(cudaMemcpyAsync(h_scratch, d_scratch, words * 8, cudaMemcpyDeviceToHost, st));
@@ -260,8 +423,31 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
   const bool want_l = which == 0 ? g->label != nullptr : (which & 2) != 0;
   int rc = FW_OK;
   auto body = [&]() -> int {
-    for (int64_t v = 0; v < g->V; ++v)
-      e->max_degree = std::max(e->max_degree, fw::row_begin(g, v + 1) - fw::row_begin(g, v));
+    std::vector<int64_t> hub_deg;
+    for (int64_t v = 0; v < g->V; ++v) {
+      const int64_t dg = fw::row_begin(g, v + 1) - fw::row_begin(g, v);
+      e->max_degree = std::max(e->max_degree, dg);
+      if (dg >= kHubMinDegree) hub_deg.push_back(dg);
+    }
+    // hubs: every vertex of at least kHubMinDegree neighbours (the walk kernel of a hub-batched call
+    // relies on every other row fitting one 4 KB stage); a graph with more than kHubMax of them
+    // runs without hub batching
+    const int64_t hub_t = kHubMinDegree;
+    std::vector<int32_t> hub_ids;
+    if (!hub_deg.empty() && (int64_t)hub_deg.size() <= kHubMax && g->V < INT32_MAX)
+      for (int64_t v = 0; v < g->V; ++v)
+        if (fw::row_begin(g, v + 1) - fw::row_begin(g, v) >= hub_t) hub_ids.push_back((int32_t)v);
+    if (!hub_ids.empty() && hub_t < ((int64_t)1 << 31)) {
+      e->n_hubs = (int32_t)hub_ids.size();
+      e->hub_min_degree = (uint32_t)hub_t;
+      FW_CUDA(cudaMalloc(&e->d_hub_ids, hub_ids.size() * 4));
+      FW_CUDA(cudaMemcpy(e->d_hub_ids, hub_ids.data(), hub_ids.size() * 4, cudaMemcpyHostToDevice));
+      FW_CUDA(cudaMalloc(&e->d_hub_cnt, hub_ids.size() * 8));
+      FW_CUDA(cudaMalloc(&e->d_hub_base, hub_ids.size() * 4));
+      FW_CUDA(cudaMalloc(&e->d_hub_fill, hub_ids.size() * 4));
+      FW_CUDA(cudaMalloc(&e->d_ctl, 2 * sizeof(HubCtl)));
+      FW_CUDA(cudaMallocHost(&e->h_ctl, 64));
+    }
     if (want_w && !g->weight) return fw::fail(FW_ERR_ARG, "graph has no weights");
     if (want_l && !g->label) return fw::fail(FW_ERR_ARG, "graph has no labels");
     const size_t xb = (size_t)(g->xadj_bits / 8) * (size_t)(g->V + 2);
@@ -293,6 +479,10 @@ extern "C" void fw_engine_destroy(fw_engine* e) {
   cudaFree(e->d_xadj); cudaFree(e->d_adj); cudaFree(e->d_weight); cudaFree(e->d_label);
   cudaFree(e->d_scratch);
   if (e->h_scratch) cudaFreeHost(e->h_scratch);
+  cudaFree(e->d_hub_ids); cudaFree(e->d_hub_cnt); cudaFree(e->d_hub_base); cudaFree(e->d_hub_fill); cudaFree(e->d_ctl);
+  if (e->h_ctl) cudaFreeHost(e->h_ctl);
+  cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
+  for (int i = 0; i < 2; ++i) { cudaFree(e->d_park_hub[i]); cudaFree(e->d_park_qi[i]); }
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_starts[i]); cudaFree(e->d_result[i]); }
   if (e->stream) cudaStreamDestroy(e->stream);
   if (e->stream2) cudaStreamDestroy(e->stream2);
@@ -303,6 +493,19 @@ extern "C" void fw_engine_destroy(fw_engine* e) {
 extern "C" int fw_engine_set_sharing(fw_engine* e, int mode) {
   if (!e || mode < -1 || mode > 1) return fw::fail(FW_ERR_ARG, "fw_engine_set_sharing: mode must be -1, 0 or 1");
   e->sharing = mode;
+  return FW_OK;
+}
+
+extern "C" int fw_engine_set_hub_batching(fw_engine* e, int mode) {
+  if (!e || mode < -1 || mode > 1) return fw::fail(FW_ERR_ARG, "fw_engine_set_hub_batching: mode must be -1, 0 or 1");
+  e->hub_mode = mode;
+  return FW_OK;
+}
+
+extern "C" int fw_engine_hubs(const fw_engine* e, int32_t* n_hubs, uint32_t* min_degree) {
+  if (!e) return fw::fail(FW_ERR_ARG, "fw_engine_hubs: null engine");
+  if (n_hubs) *n_hubs = e->n_hubs;
+  if (min_degree) *min_degree = e->hub_min_degree;
   return FW_OK;
 }
 
@@ -325,12 +528,13 @@ extern "C" int fw_walk_device(fw_engine* e, const fw_walk_params* p, const int32
   rc = ensure_scratch(e, p->d);
   if (rc) return rc;
   cudaStream_t st = stream ? (cudaStream_t)stream : e->stream;
-  rc = enqueue_walk(e, p, starts_dev, n, result_dev, st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch);
+  int launches = 0;
+  rc = enqueue_walk(e, p, starts_dev, n, result_dev, st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch, &launches);
   if (rc) return rc;
   FW_CUDA(cudaStreamSynchronize(st));
   float ms = 0.f;
   FW_CUDA(cudaEventElapsedTime(&ms, e->ev[0], e->ev[1]));
-  rc = collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
+  rc = collect(e->h_scratch, p->d, ms, launches, stats, len_hist, false);
   if (stats) stats->total_ms = ms;
   return rc;
 }
@@ -352,7 +556,8 @@ extern "C" int fw_walk(fw_engine* e, const fw_walk_params* p, const int32_t* sta
   cudaStream_t st = e->stream;
   FW_CUDA(cudaEventRecord(e->ev[2], st));
   if (n > 0) FW_CUDA(cudaMemcpyAsync(e->d_starts[0], starts_host, (size_t)n * 4, cudaMemcpyHostToDevice, st));
-  rc = enqueue_walk(e, p, e->d_starts[0], n, e->d_result[0], st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch);
+  int launches = 0;
+  rc = enqueue_walk(e, p, e->d_starts[0], n, e->d_result[0], st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch, &launches);
   if (rc) return rc;
   if (n > 0) FW_CUDA(cudaMemcpyAsync(result_host, e->d_result[0], cells * 4, cudaMemcpyDeviceToHost, st));
   FW_CUDA(cudaEventRecord(e->ev[3], st));
@@ -360,7 +565,7 @@ extern "C" int fw_walk(fw_engine* e, const fw_walk_params* p, const int32_t* sta
   float ms = 0.f, total = 0.f;
   FW_CUDA(cudaEventElapsedTime(&ms, e->ev[0], e->ev[1]));
   FW_CUDA(cudaEventElapsedTime(&total, e->ev[2], e->ev[3]));
-  rc = collect(e->h_scratch, p->d, ms, n > 0 ? 1 : 0, stats, len_hist, false);
+  rc = collect(e->h_scratch, p->d, ms, launches, stats, len_hist, false);
   if (stats) stats->total_ms = total;
   return rc;
 }
@@ -407,13 +612,14 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
   cudaEvent_t t0 = e->ev[4], t1 = e->ev[5];
   cudaEventRecord(t0, streams[0]);
   bool pending[2] = {false, false};
+  int batch_launches[2] = {0, 0};
   auto drain = [&](int s) -> int {
     if (!pending[s]) return FW_OK;
     FW_CUDA(cudaStreamSynchronize(streams[s]));
     float ms = 0.f;
     FW_CUDA(cudaEventElapsedTime(&ms, evs[s][0], evs[s][1]));
     pending[s] = false;
-    return collect(hsc[s], p->d, ms, 1, stats, len_hist, true);
+    return collect(hsc[s], p->d, ms, batch_launches[s], stats, len_hist, true);
   };
   int which = 0;
   fw_walk_params bp = *p;
@@ -425,7 +631,8 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
     bp.query_id_base = p->query_id_base + (uint64_t)off * (p->query_id_stride ? p->query_id_stride : 1);
     cudaError_t err = cudaMemcpyAsync(e->d_starts[which], starts_host + off, (size_t)m * 4, cudaMemcpyHostToDevice, st);
     if (err != cudaSuccess) { rc = fw::fail(FW_ERR_CUDA, "H2D copy failed: %s", cudaGetErrorString(err)); break; }
-    rc = enqueue_walk(e, &bp, e->d_starts[which], m, e->d_result[which], st, evs[which][0], evs[which][1], dsc[which], hsc[which]);
+    rc = enqueue_walk(e, &bp, e->d_starts[which], m, e->d_result[which], st, evs[which][0], evs[which][1], dsc[which], hsc[which],
+                      &batch_launches[which]);
     if (rc) break;
     err = cudaMemcpyAsync(pinned + (size_t)off * D, e->d_result[which], (size_t)m * D * 4, cudaMemcpyDeviceToHost, st);
     if (err != cudaSuccess) { rc = fw::fail(FW_ERR_CUDA, "D2H copy failed: %s", cudaGetErrorString(err)); break; }

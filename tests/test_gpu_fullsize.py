@@ -19,7 +19,7 @@ def _check(g, app, kw, starts, chunks, chunk_len, seed=1337):
     eng = fw.Engine(g, 0)
     prm = fw.make_params(app, seed=seed, **kw)
     res, st, hist = eng.walk(prm, starts, want_hist=True)
-    assert st.device_status == 0 and st.launches == 1
+    assert st.device_status == 0 and st.launches >= 1  # a hub-batched call is a series of launches
     # a second run gives the same walks
     res2, st2 = eng.walk(prm, starts)
     assert st2.steps == st.steps and st2.scanned == st.scanned

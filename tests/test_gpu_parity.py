@@ -17,10 +17,11 @@ APPS = [
 MODES = [fw.GROUP_STRIP, fw.GROUP_EDGE]
 
 
-def run_both(arrs, app, kw, starts, mode, seed=1337, base=0, sharing=-1, managed=False):
+def run_both(arrs, app, kw, starts, mode, seed=1337, base=0, sharing=-1, managed=False, hub=-1):
     g = fw.Graph.from_arrays(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"])
     eng = fw.Engine(g, 0, managed=managed)
     eng.set_sharing(sharing)
+    eng.set_hub_batching(hub)
     prm = fw.make_params(app, group_mode=mode, seed=seed, query_id_base=base, **kw)
     res, st, hist = eng.walk(prm, starts, want_hist=True)
     ref, steps, scanned, rhist = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], app,
@@ -37,7 +38,7 @@ def assert_same(out):
     assert st.steps == steps and st.scanned == scanned
     assert (hist == rhist).all()
     assert st.device_status == 0
-    assert st.launches == 1
+    assert st.launches >= 1  # one kernel, or the series of launches of a hub-batched call
 
 
 @pytest.mark.parametrize("mode", MODES)
@@ -96,6 +97,32 @@ def test_star_hub_shared_between_warps(app, kw, n):
     assert_same(run_both(arrs, app, kw, starts, fw.GROUP_STRIP, seed=5, sharing=1))
 
 
+@pytest.mark.parametrize("hub", [0, -1, 1])
+@pytest.mark.parametrize("app,kw", APPS[:2])
+def test_hub_batching_on_and_off(app, kw, hub):
+    """Walkers that meet at a vertex of 1,024 or more neighbours share one sweep of its row (a walk
+    call is then a series of launches); with it switched off every walker sweeps for itself in one
+    kernel.  Both give the golden walker's walks: rows around the hub limit, a 100,000-leaf star
+    where every walker is at the hub every other step, queries that start at hubs, PPR's stop test
+    after a hub step, 32- and 64-bit offsets.  hub = 1 batches down to the last walker; the default
+    leaves the last few to one launch that does not batch."""
+    arrs = graphs.ragged(np.int64 if app == fw.APP_PPR else np.uint32)
+    starts = np.concatenate([np.arange(arrs["n_rows"])] * 3).astype(np.int32)
+    kw2 = dict(kw)
+    kw2["d"] = 15
+    out = run_both(arrs, app, kw2, starts, fw.GROUP_STRIP, seed=21, base=7, hub=hub)
+    assert_same(out)
+    assert (out[1].launches == 1) == (hub == 0)
+    star = graphs.star()
+    starts = np.zeros(3000, dtype=np.int32)
+    starts[1::3] = np.arange(1, 3000, 3) % 1000 + 1
+    out = run_both(star, app, kw2, starts, fw.GROUP_STRIP, seed=22, hub=hub)
+    assert_same(out)
+    assert (out[1].launches == 1) == (hub == 0)
+    # d = 1: every walker that starts at the hub ends right after the hub step
+    assert_same(run_both(star, app, dict(kw, d=1), np.zeros(100, dtype=np.int32), fw.GROUP_STRIP, hub=hub))
+
+
 @pytest.mark.parametrize("app,kw", APPS)
 def test_rmat16_many_queries(app, kw):
     g = fw.rmat(16, 16 << 16, weight_range=(0.0, 1.0), n_labels=5)
@@ -142,14 +169,14 @@ def test_shards_union_equals_single_run():
                                 starts[1::3], batch_size=100)
     assert (strided == full[1::3]).all()
     out, st = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=128)
-    assert (out == full).all() and st.launches == 8
+    assert (out == full).all() and st.launches >= 8
     auto, st_auto = eng.walk_batch(fw.make_params(fw.APP_DEEPWALK, d=40), starts, batch_size=0)  # autobatch
-    assert (auto == full).all() and st_auto.launches == 1
+    assert (auto == full).all() and st_auto.launches >= 1
     into = np.full((1000, 41), -9, dtype=np.int32)
     st2 = fw.WalkStats()
     prm = fw.make_params(fw.APP_DEEPWALK, d=40)
     rc = fw.lib().fw_walk_batch_into(eng._h, prm[0], starts.ctypes.data, 1000, 300, 512, into.ctypes.data, st2, None)
-    assert rc == 0 and (into == full).all() and st2.launches == 4 and st2.steps == st.steps
+    assert rc == 0 and (into == full).all() and st2.launches >= 4 and st2.steps == st.steps
     eng.close()
 
 
