@@ -78,7 +78,7 @@ def lib():
         L.fw_engine_device.argtypes = [vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         L.fw_engine_set_sharing.argtypes = [vp, ctypes.c_int]
         L.fw_engine_set_hub_batching.argtypes = [vp, ctypes.c_int]
-        L.fw_engine_hubs.argtypes = [vp, ctypes.POINTER(i32), ctypes.POINTER(ctypes.c_uint32)]
+        L.fw_engine_hubs.argtypes = [vp, ctypes.c_int, ctypes.POINTER(i32), ctypes.POINTER(ctypes.c_uint32)]
         L.fw_walk_device.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, vp,
                                      ctypes.POINTER(WalkStats), vp]
         L.fw_walk.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, ctypes.POINTER(WalkStats), vp]
@@ -222,10 +222,11 @@ class Engine:
         walker.  Walkers that meet at a hub share one sweep of its row."""
         _check(lib().fw_engine_set_hub_batching(self._h, mode))
 
-    def hubs(self):
-        """(number of hub vertices, row length from which a vertex is a hub)."""
+    def hubs(self, which=0):
+        """(number of hub vertices, row length from which a vertex is a hub) for the limit of
+        1,016 neighbours (which=0) or of 504 (which=1)."""
         n, t = ctypes.c_int32(), ctypes.c_uint32()
-        _check(lib().fw_engine_hubs(self._h, n, t))
+        _check(lib().fw_engine_hubs(self._h, which, n, t))
         return n.value, t.value
 
     def walk(self, params, starts, want_hist=False):

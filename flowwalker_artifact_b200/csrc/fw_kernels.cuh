@@ -26,7 +26,7 @@ constexpr int kMaxSchema = 64;
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = 32 * kWarpsPerCta;
 #ifndef FW_SLOTS
-#define FW_SLOTS 8
+#define FW_SLOTS 16
 #endif
 #ifndef FW_N2V_SLOTS
 #define FW_N2V_SLOTS 1
@@ -84,8 +84,11 @@ struct HubArgs {
   int32_t* next_list;       // hub kernel: walkers that go on from a vertex that is not a hub
   uint32_t* next_n;
   const int32_t* bucket;    // hub kernel: the parked queries grouped by hub
-  const int4* items;        // (hub index, first entry in bucket, entries <= 32, unused) per batch
+  const int4* items;        // per item: hub index, first entry in bucket, entries | part << 8 | parts << 16, group
   const uint32_t* items_n;
+  const uint16_t* hub_parts;  // parts the sweep of each hub's row is split into (1: one warp sweeps all of it)
+  unsigned long long* best64; // split rows: smallest (key << 32 | strip id) per bucket entry over the parts done
+  uint32_t* part_done;        // split rows: parts done, per group (index of the group's first item)
   unsigned long long* work; // work counter of this launch
 };
 
@@ -562,6 +565,15 @@ __device__ __forceinline__ bool ring_sub(const WalkArgs& a, const StepCtx& c, ui
 // row's first and last supergroup are reduced with the boundary masks, the ones in between bare.
 constexpr uint32_t kHalfBytes = 2u * kSubBytes;      // one stage
 constexpr uint32_t kHalfQuads = 2u * fw::kQuadsPerSub;
+
+// Hub batching: a vertex is a hub from a limit of neighbours on.  The walk kernel of a hub-batched
+// call only meets rows below the limit and stages each of them whole: a row of fewer than
+// 4 Q - 7 neighbours is at most Q quads however it is aligned.  Two limits are compiled, the
+// lower one for calls that bring enough walkers per hub to fill its batches:
+// 504 (rows of at most 128 quads, 2 KB stages, four CTAs per SM) and 1,016 (256 quads, 4 KB, three).
+constexpr uint32_t kHubLimitLow = 504, kHubLimitHigh = 1016;
+__host__ __device__ constexpr uint32_t staged_quads(uint32_t limit) { return (limit + 7u + 3u) / 4u; }
+static_assert(staged_quads(kHubLimitLow) == 128u && staged_quads(kHubLimitHigh) == 256u, "one or two sub-blocks per lane");
 
 // Ring bytes per warp by the kernel's app: node2vec keeps the ring of two 2 KB stages.
 template <int APP>
@@ -1322,10 +1334,10 @@ constexpr int min_blocks() {
   return MODE == FW_GROUP_EDGE ? 2 : APP == FW_APP_NODE2VEC ? FW_N2V_MIN_BLOCKS : FW_MIN_BLOCKS;
 }
 
-// The strip sampler on a row of at most 256 quads (one 4 KB stage: every row that is not a hub's)
+// The strip sampler on a row of at most SQ quads (one stage: every row that is not a hub's)
 // that was staged ahead into stage T of the warp's ring: the copy of the next slot's row is in
 // flight while this one is reduced.  Same strips, keys and pick as sample_row_warp.
-template <int APP, bool CLEAN>
+template <int APP, bool CLEAN, uint32_t SQ>
 __device__ __forceinline__ uint32_t sample_staged(const WalkArgs& a, const StepCtx& c, uint32_t step, uint32_t qlo,
                                                   uint32_t qhi, uint32_t lane, Ring& ring, const unsigned char* ring_ptr,
                                                   uint32_t T) {
@@ -1334,7 +1346,7 @@ __device__ __forceinline__ uint32_t sample_staged(const WalkArgs& a, const StepC
   const uint32_t ok = mbar_wait_inline(ring.bar + 8u * T, (ring.parity >> T) & 1u);
   ring.parity ^= 1u << T;
   if (!__all_sync(0xFFFFFFFFu, ok != 0u)) { ring.failed = true; return 0xFFFFFFFFu; }
-  const unsigned char* stage = ring_ptr + T * kHalfBytes;
+  const unsigned char* stage = ring_ptr + T * (16u * SQ);
   const int4* st = reinterpret_cast<const int4*>(stage) + lane;
   Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
   if (c.nq <= 32u) {
@@ -1362,7 +1374,7 @@ __device__ __forceinline__ uint32_t sample_staged(const WalkArgs& a, const StepC
   // strip l = quads 32 j + l, j < 8: sub-blocks 0 and 1 of supergroup 0 (the others are empty, and
   // adding their zeros leaves (A0+A1)+(A2+A3) = A0+A1 bit for bit).  Quads past the row, stale
   // bytes of the stage included, are masked.
-  float S[8];
+  float S[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     float4 v = plain_bias<APP, CLEAN>(st[32 * j], c.want);
@@ -1370,7 +1382,7 @@ __device__ __forceinline__ uint32_t sample_staged(const WalkArgs& a, const StepC
     S[j] = sum4(v);
   }
   float W = sum_strip(S);
-  if (c.nq > (uint32_t)fw::kQuadsPerSub) {  // warp-uniform
+  if (SQ > (uint32_t)fw::kQuadsPerSub && c.nq > (uint32_t)fw::kQuadsPerSub) {  // warp-uniform
 #pragma unroll
     for (int j = 4; j < 8; ++j) {
       float4 v = plain_bias<APP, CLEAN>(st[32 * j], c.want);
@@ -1387,10 +1399,11 @@ __device__ __forceinline__ uint32_t sample_staged(const WalkArgs& a, const StepC
                                        __shfl_sync(0xFFFFFFFFu, best.W, (int)B), lane, stage);
 }
 
-// The row of c (at most 256 quads) into stage T (lane 0 only calls this).
+// The row of c (at most SQ quads) into stage T (lane 0 only calls this).
+template <uint32_t SQ>
 __device__ __forceinline__ void row_fill(const StepCtx& c, const Ring& ring, uint32_t T) {
   mbar_expect_tx(ring.bar + 8u * T, 16u * c.nq);
-  bulk_g2s(ring.data + T * kHalfBytes, c.prim, 16u * c.nq, ring.bar + 8u * T);
+  bulk_g2s(ring.data + T * (16u * SQ), c.prim, 16u * c.nq, ring.bar + 8u * T);
 }
 
 // Index of hub vertex v in the ascending list ids[0, n) (v is known to be in it).
@@ -1419,14 +1432,21 @@ __device__ __forceinline__ void hub_park(const HubArgs& hb, long long qi, int32_
 // that is not one).
 // The tail of the series (HUBS == kHubTail): when few walkers are left parked, batches would be
 // nearly empty; one launch then walks them to the end, every walker sweeping for itself.
-constexpr int kHubOff = 0, kHubPark = 1, kHubTail = 2;
+constexpr int kHubOff = 0, kHubPark = 1, kHubTail = 2, kHubParkLow = 3;  // kHubPark: the limit of 1,016; kHubParkLow: of 504
+__host__ __device__ constexpr bool hub_parks(int hubs) { return hubs == kHubPark || hubs == kHubParkLow; }
+__host__ __device__ constexpr uint32_t hub_staged_quads(int hubs) { return staged_quads(hubs == kHubParkLow ? kHubLimitLow : kHubLimitHigh); }
+template <int APP, int MODE, bool CLEAN, typename OffT, int HUBS>
+constexpr int walk_min_blocks() {
+  return HUBS == kHubParkLow ? 4 : HUBS == kHubPark ? 3 : min_blocks<APP, MODE, CLEAN, OffT>();
+}
 template <int APP, int MODE, bool CLEAN, typename OffT, int HUBS = kHubOff>
-__global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()) walk_kernel(const __grid_constant__ WalkArgs a) {
+__global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, OffT, HUBS>()) walk_kernel(const __grid_constant__ WalkArgs a) {
   extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][kStages];
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-  constexpr uint32_t kRingPerWarp = MODE != FW_GROUP_EDGE ? ring_bytes<APP>() : 0u;
+  constexpr uint32_t kStagedQuads = hub_staged_quads(HUBS);
+  constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_EDGE ? 0u : hub_parks(HUBS) ? 2u * 16u * kStagedQuads : ring_bytes<APP>();
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
   Ring ring;
@@ -1530,13 +1550,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
       rlen = e > b ? (uint32_t)(e - b) : 0u;
       if (rlen == 0u) {
         st = 2u;  // dead end
-      } else if (HUBS == kHubPark && rlen >= a.hub.min_degree) {
+      } else if (hub_parks(HUBS) && rlen >= a.hub.min_degree) {
         hub_park(a.hub, qi, k, cur);  // the slot is free again; the hub launch takes the walker from here
         st = 0u;
       }
     }
     // ---- the weighted pick: the whole warp on one slot's row at a time ----
-    if constexpr (HUBS == kHubPark) {
+    if constexpr (hub_parks(HUBS)) {
       // Every row here is shorter than a hub's: one 4 KB stage holds it.  The two stages take
       // turns, so the next slot's row is on its way while this slot's is reduced.
       uint32_t m = __ballot_sync(0xFFFFFFFFu, st == 1u);
@@ -1560,7 +1580,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
         StepCtx c;
         uint32_t ks, ql, qh, T = 0u;
         slot_ctx(s, c, ks, ql, qh);
-        if (lane == 0) row_fill(c, ring, T);
+        if (lane == 0) row_fill<kStagedQuads>(c, ring, T);
         for (;;) {
           int s2 = -1;
           StepCtx c2;
@@ -1569,9 +1589,9 @@ __global__ void __launch_bounds__(kThreads, min_blocks<APP, MODE, CLEAN, OffT>()
             s2 = __ffs((int)m) - 1;
             m &= m - 1u;
             slot_ctx(s2, c2, ks2, ql2, qh2);
-            if (lane == 0) row_fill(c2, ring, T ^ 1u);
+            if (lane == 0) row_fill<kStagedQuads>(c2, ring, T ^ 1u);
           }
-          const uint32_t rel = sample_staged<APP, CLEAN>(a, c, ks, ql, qh, lane, ring, ring_ptr, T);
+          const uint32_t rel = sample_staged<APP, CLEAN, kStagedQuads>(a, c, ks, ql, qh, lane, ring, ring_ptr, T);
           if (ring.failed) break;
           if ((int)lane == s) my_rel = rel;
           if (s2 < 0) break;
@@ -1757,6 +1777,34 @@ __device__ __forceinline__ uint32_t pick_lane(const StepCtx& c, uint32_t B, uint
   return 4u * (32u * (blk0 + (cnt >> 2)) + lB) + (cnt & 3u);
 }
 
+// Total bias of strip B by one lane, in the canonical order of the sweep (the same bits).
+template <int APP, bool CLEAN>
+__device__ __forceinline__ float strip_total_lane(const StepCtx& c, uint32_t B) {
+  const uint32_t sB = B >> 5, lB = B & 31u;
+  float A[4];
+#pragma unroll 1
+  for (uint32_t i = 0; i < 4u; ++i) {
+    float S[4];
+#pragma unroll
+    for (uint32_t j = 0; j < 4u; ++j) {
+      const uint32_t q = sB * fw::kQuadsPerSuper + i * fw::kQuadsPerSub + 32u * j + lB;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (q < c.nq) {
+        v = plain_bias<APP, CLEAN>(__ldg(c.prim + q), c.want);
+        mask_quad(v, q, c.head, c.tail);
+      }
+      S[j] = sum4(v);
+    }
+    A[i] = sum_strip(S);
+  }
+  return __fadd_rn(__fadd_rn(A[0], A[1]), __fadd_rn(A[2], A[3]));
+}
+
+// Supergroups per part of a split row (a multiple of three: a Philox block serves three).
+__host__ __device__ constexpr uint32_t hub_part_supers(uint32_t supers, uint32_t parts) {
+  return ((supers + parts - 1u) / parts + 2u) / 3u * 3u;
+}
+
 template <int APP, bool CLEAN, typename OffT>
 __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __grid_constant__ WalkArgs a) {
   static_assert(APP == FW_APP_DEEPWALK || APP == FW_APP_PPR, "strip totals must not depend on the walker");
@@ -1793,7 +1841,8 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
     if (lane == 0) item = atomicAdd(a.hub.work, 1ull);
     item = __shfl_sync(0xFFFFFFFFu, item, 0);
     if (item >= (unsigned long long)n_items) break;
-    const int4 it = __ldg(a.hub.items + item);  // hub index, first entry, entries
+    const int4 it = __ldg(a.hub.items + item);  // hub index, first entry, entries | part << 8 | parts << 16, group
+    const uint32_t n_in = (uint32_t)it.z & 0xFFu, part = ((uint32_t)it.z >> 8) & 0xFFu, parts = (uint32_t)it.z >> 16;
     const int32_t v = __ldg(a.hub.hub_ids + it.x);
     const int64_t b = (int64_t)__ldg(xadj + v);
     const uint32_t len = (uint32_t)((int64_t)__ldg(xadj + v + 1) - b);
@@ -1806,7 +1855,7 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
     c.nq = (c.tail + 3u) >> 2;
     c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = nullptr;
     // the walker this lane stands for
-    const bool have = lane < (uint32_t)it.z;
+    const bool have = lane < n_in;
     const long long qi = have ? (long long)__ldg(a.hub.bucket + it.y + lane) : 0;
     int32_t k = have ? a.hub.kstate[qi] : 0;
     const uint64_t qid = a.qid_base + (uint64_t)qi * a.qid_stride;
@@ -1814,22 +1863,27 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
     const uint32_t c1 = (uint32_t)k | (fw::kPurposeScan << 28);
     Best best{0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0.0f};
 
-    // ---- one sweep of the row; the walkers' keys after every third supergroup ----
+    // ---- one sweep of the row (of this item's part of it); the walkers' keys after every third supergroup ----
     const uint32_t n_half = (c.nq + kHalfQuads - 1u) / kHalfQuads;
     const uint32_t end_super = ((n_half + 1u) >> 1) - 1u;
-    if (lane == 0) {
-      half_fill(c, ring, 0u);
-      if (n_half > 1u) half_fill(c, ring, 1u);
+    // a very long row is split into parts of whole Philox blocks (three supergroups each), one item per part
+    const uint32_t per = hub_part_supers(end_super + 1u, parts);
+    const uint32_t s_lo = part * per, s_last = min(end_super, s_lo + per - 1u);
+    const uint32_t h_end = min(n_half, 2u * (s_last + 1u));
+    const bool any = s_lo <= end_super;  // rounding can leave the last parts of a row empty
+    if (any && lane == 0) {
+      half_fill(c, ring, 2u * s_lo);
+      if (2u * s_lo + 1u < h_end) half_fill(c, ring, 2u * s_lo + 1u);
     }
     float W0 = 0.0f, W1 = 0.0f, W2 = 0.0f;
-    uint32_t g = 0, m = 0;
+    uint32_t g = s_lo / 3u, m = 0;
 #pragma unroll 1
-    for (uint32_t sg = 0;; ++sg) {
-      const bool last = sg == end_super;
+    for (uint32_t sg = s_lo; any; ++sg) {
+      const bool last = sg == s_last;
       float W;
       bool ok;
-      if (sg == 0u || last) ok = super_turn<APP, CLEAN, true>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
-      else ok = super_turn<APP, CLEAN, false>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
+      if (sg == 0u || sg == end_super) ok = super_turn<APP, CLEAN, true>(c, sg, n_half, h_end, lane, ring, lane_ptr, W);
+      else ok = super_turn<APP, CLEAN, false>(c, sg, n_half, h_end, lane, ring, lane_ptr, W);
       if (!ok) { ring.failed = true; break; }
       if (m == 0u) W0 = W; else if (m == 1u) W1 = W; else W2 = W;
       if (m == 2u || last) {
@@ -1852,6 +1906,24 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
       if (last) break;
     }
     if (ring.failed) break;
+    if (parts > 1u) {
+      // Split row: every part folds its walkers' best (key, strip id) into the group's words; the
+      // part that finds all the others done goes on for the group (nobody waits for anybody).
+      if (have && best.id != 0xFFFFFFFFu)
+        atomicMin(a.hub.best64 + it.y + lane, ((unsigned long long)best.key << 32) | best.id);
+      __threadfence();
+      unsigned int before = 0;
+      if (lane == 0) before = atomicAdd(a.hub.part_done + it.w, 1u);
+      if (__shfl_sync(0xFFFFFFFFu, before, 0) != parts - 1u) continue;
+      __threadfence();
+      const unsigned long long w = have ? atomicMin(a.hub.best64 + it.y + lane, ~0ull) : ~0ull;  // a coherent read
+      best.key = (uint32_t)(w >> 32);
+      best.id = (uint32_t)w;
+      if (have && best.id != 0xFFFFFFFFu) {  // pick word and total of the winning strip, formed again
+        best.pick = fw::philox4x32_10(((best.id >> 5) / 3u) * 32u + (best.id & 31u), c1, qlo, qhi, a.rk).w;
+        best.W = strip_total_lane<APP, CLEAN>(c, best.id);
+      }
+    }
 
     // ---- every walker takes its step ----
     bool fin = false;
@@ -1932,7 +2004,8 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
 // per 32 walkers of a hub, the counts and the scatter cursors back to zero.  One CTA of kPlanThreads.
 constexpr int kPlanThreads = 1024;
 __global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, uint32_t* base, uint32_t* fill, int4* items,
-                                                                uint32_t* items_n, int n_hubs) {
+                                                                uint32_t* items_n, const uint16_t* __restrict__ parts,
+                                                                uint32_t* part_done, int n_hubs) {
   __shared__ uint32_t s_cnt[kPlanThreads], s_bat[kPlanThreads];
   const int t = threadIdx.x;
   const int per = (n_hubs + kPlanThreads - 1) / kPlanThreads;
@@ -1940,7 +2013,7 @@ __global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, u
   uint32_t my_cnt = 0, my_bat = 0;
   for (int h = h0; h < h1; ++h) {
     my_cnt += cnt[h];
-    my_bat += (cnt[h] + 31u) >> 5;
+    my_bat += ((cnt[h] + 31u) >> 5) * parts[h];
   }
   s_cnt[t] = my_cnt;
   s_bat[t] = my_bat;
@@ -1954,9 +2027,14 @@ __global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, u
   }
   uint32_t at = s_cnt[t] - my_cnt, ib = s_bat[t] - my_bat;
   for (int h = h0; h < h1; ++h) {
-    const uint32_t n = cnt[h];
+    const uint32_t n = cnt[h], np = parts[h];
     base[h] = at;
-    for (uint32_t off = 0; off < n; off += 32u) items[ib++] = make_int4(h, (int)(at + off), (int)min(32u, n - off), 0);
+    for (uint32_t off = 0; off < n; off += 32u) {
+      const uint32_t group = ib;
+      part_done[group] = 0u;
+      for (uint32_t p = 0; p < np; ++p)
+        items[ib++] = make_int4(h, (int)(at + off), (int)(min(32u, n - off) | (p << 8) | (np << 16)), (int)group);
+    }
     at += n;
     cnt[h] = 0u;
     fill[h] = 0u;
@@ -1988,13 +2066,17 @@ inline KernelFn pick_hub_serve(bool clean, int xadj_bits) {
   if (xadj_bits == 64) return clean ? (KernelFn)hub_kernel<APP, true, int64_t> : (KernelFn)hub_kernel<APP, false, int64_t>;
   return clean ? (KernelFn)hub_kernel<APP, true, uint32_t> : (KernelFn)hub_kernel<APP, false, uint32_t>;
 }
-// which: 0 the walk kernel that parks at hubs, 1 the hub kernel, 2 the walk kernel of the tail
+// which: 0 the walk kernel that parks at hubs of 1,016 neighbours, 3 of 504, 1 the hub kernel,
+// 2 the walk kernel of the tail
+template <int APP>
+inline KernelFn pick_hub_kernel_of(int which, bool clean, int xadj_bits) {
+  return which == 1 ? pick_hub_serve<APP>(clean, xadj_bits)
+       : which == 2 ? pick_hub_walk<APP, kHubTail>(clean, xadj_bits)
+       : which == 3 ? pick_hub_walk<APP, kHubParkLow>(clean, xadj_bits) : pick_hub_walk<APP, kHubPark>(clean, xadj_bits);
+}
 inline KernelFn pick_hub_kernel(int app, int which, bool clean, int xadj_bits) {
-  if (app == FW_APP_PPR)
-    return which == 1 ? pick_hub_serve<FW_APP_PPR>(clean, xadj_bits)
-         : which == 2 ? pick_hub_walk<FW_APP_PPR, kHubTail>(clean, xadj_bits) : pick_hub_walk<FW_APP_PPR, kHubPark>(clean, xadj_bits);
-  return which == 1 ? pick_hub_serve<FW_APP_DEEPWALK>(clean, xadj_bits)
-       : which == 2 ? pick_hub_walk<FW_APP_DEEPWALK, kHubTail>(clean, xadj_bits) : pick_hub_walk<FW_APP_DEEPWALK, kHubPark>(clean, xadj_bits);
+  if (app == FW_APP_PPR) return pick_hub_kernel_of<FW_APP_PPR>(which, clean, xadj_bits);
+  return pick_hub_kernel_of<FW_APP_DEEPWALK>(which, clean, xadj_bits);
 }
 
 template <int APP, int MODE, bool CLEAN>
@@ -2018,6 +2100,11 @@ inline KernelFn pick_kernel(int app, int mode, bool clean, bool shared, int xadj
     default:  // MetaPath biases are 0/1: nothing to clamp
       return pick_mode<FW_APP_METAPATH>(mode, true, shared, xadj_bits);
   }
+}
+
+// Dynamic shared memory of a CTA of the walk kernel of a hub-batched call.
+inline size_t hub_walk_smem_bytes(uint32_t hub_limit, int d, bool hist_in_smem) {
+  return (size_t)kWarpsPerCta * 2u * 16u * staged_quads(hub_limit) + (hist_in_smem ? (size_t)(d + 1) * 4 : 0);
 }
 
 // Dynamic shared memory of one CTA: the warps' rings, then the histogram.

@@ -38,8 +38,13 @@ static constexpr int64_t kSharingAutoDegree = 262144;
 
 // Hub batching: vertices of at least this many neighbours are hubs (about the reference's limit
 // between its warp and its block sampler, 1,024: include/walker.cuh:29).
-static constexpr int64_t kHubMinDegree = 1016;  // a row below it is at most 256 quads (4 KB) however it is aligned
+// A call uses the lower hub limit when it brings at least this many queries per hub of that limit
+// (measured: R-MAT scale 22, all-vertex queries, 168 per hub: 57 ms against 61 with the higher limit;
+// scale 24, 10^7 PPR queries, about 50 per hub: 31 ms against 24).
+static constexpr int64_t kHubDenseQueries = 100;
 static constexpr int64_t kHubMax = (int64_t)1 << 22;
+static constexpr int64_t kHubPartSupers = 48;  // supergroups (98,304 neighbours) of a hub's row per sweeping warp, about
+static constexpr int64_t kHubMaxParts = 64;
 static constexpr int64_t kHubTailMin = 2048;   // parked walkers below which a call goes to its tail launch ...
 static constexpr int64_t kHubTailShare = 64;   // ... or below this share of the call's queries
 
@@ -78,12 +83,16 @@ struct fw_engine {
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   // hub batching: the hub vertices and the buffers of a hub-batched call (grown on demand)
   int hub_mode = -1;           // -1: when the graph has hubs, 0: never, 1: as -1 without the tail launch
-  int32_t n_hubs = 0;
-  uint32_t hub_min_degree = 0;
-  int32_t* d_hub_ids = nullptr;
-  uint32_t* d_hub_cnt = nullptr;   // [2][n_hubs] parked walkers per hub, this round and the next
-  uint32_t* d_hub_base = nullptr;  // [n_hubs]
-  uint32_t* d_hub_fill = nullptr;  // [n_hubs]
+  struct HubSet {                  // the hub vertices for one limit
+    int32_t n = 0;
+    uint32_t limit = 0;            // a vertex is a hub iff its row has at least this many edges
+    int32_t* d_ids = nullptr;      // ascending
+    uint32_t* d_cnt = nullptr;     // [2][n] parked walkers per hub, this round and the next
+    uint32_t* d_base = nullptr;    // [n]
+    uint32_t* d_fill = nullptr;    // [n]
+    uint16_t* d_parts = nullptr;   // [n] parts the sweep of a hub's row is split into
+    uint64_t parts_total = 0;      // their sum
+  } hubset[2];                     // 0: limit 1,016, 1: limit 504
   size_t hub_cap = 0;              // queries the buffers below are sized for
   int32_t* d_kstate = nullptr;
   int32_t* d_list = nullptr;
@@ -91,6 +100,9 @@ struct fw_engine {
   int32_t* d_park_qi[2] = {nullptr, nullptr};
   int32_t* d_bucket = nullptr;
   int4* d_items = nullptr;
+  size_t items_cap = 0;
+  unsigned long long* d_best64 = nullptr;  // [hub_cap]
+  uint32_t* d_part_done = nullptr;         // [items_cap]
   unsigned char* d_ctl = nullptr;  // two HubCtl blocks
   uint32_t* h_ctl = nullptr;       // pinned word the parked count travels to
   // staging for the host-buffer entry points (grown on demand)
@@ -198,9 +210,10 @@ int prepare_kernel(KernelFn fn, size_t smem, int* per_sm) {
 int ensure_hub_buffers(fw_engine* e, size_t n) {
   if (n <= e->hub_cap) return FW_OK;
   cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
+  cudaFree(e->d_best64); cudaFree(e->d_part_done);
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_park_hub[i]); cudaFree(e->d_park_qi[i]); }
   e->d_kstate = e->d_list = e->d_bucket = nullptr;
-  e->d_items = nullptr;
+  e->d_items = nullptr; e->d_best64 = nullptr; e->d_part_done = nullptr;
   e->d_park_hub[0] = e->d_park_hub[1] = e->d_park_qi[0] = e->d_park_qi[1] = nullptr;
   e->hub_cap = 0;
   const size_t cap = std::max<size_t>(n, 1024);
@@ -211,7 +224,11 @@ int ensure_hub_buffers(fw_engine* e, size_t n) {
     FW_CUDA(cudaMalloc(&e->d_park_hub[i], cap * 4));
     FW_CUDA(cudaMalloc(&e->d_park_qi[i], cap * 4));
   }
-  FW_CUDA(cudaMalloc(&e->d_items, (cap / 32 + (size_t)e->n_hubs + 1) * sizeof(int4)));
+  // every hub has at most one batch that is not full, every batch one item per part of the row
+  e->items_cap = (cap / 32) * (size_t)kHubMaxParts + (size_t)std::max(e->hubset[0].parts_total, e->hubset[1].parts_total) + 1;
+  FW_CUDA(cudaMalloc(&e->d_items, e->items_cap * sizeof(int4)));
+  FW_CUDA(cudaMalloc(&e->d_part_done, e->items_cap * 4));
+  FW_CUDA(cudaMalloc(&e->d_best64, cap * 8));
   e->hub_cap = cap;
   return FW_OK;
 }
@@ -219,15 +236,16 @@ int ensure_hub_buffers(fw_engine* e, size_t n) {
 // The launches of a hub-batched call (see hub_kernel): the walk kernel on the fresh queries, then
 // rounds of plan, scatter, hub kernel, walk kernel while walkers are parked at hubs.  Every round
 // ends with the host reading the number of parked walkers, so this returns with the walk done.
-int run_hub_batched(fw_engine* e, const fw_walk_params* p, WalkArgs a, int64_t n, cudaStream_t st, size_t smem,
-                    int* launches) {
+int run_hub_batched(fw_engine* e, const fw_engine::HubSet& hs, const fw_walk_params* p, WalkArgs a, int64_t n,
+                    cudaStream_t st, size_t smem, int* launches) {
   int rc = ensure_hub_buffers(e, (size_t)n);
   if (rc) return rc;
-  KernelFn walk_fn = pick_hub_kernel(p->app, 0, e->clean_weights, e->xadj_bits);
+  KernelFn walk_fn = pick_hub_kernel(p->app, hs.limit == kHubLimitLow ? 3 : 0, e->clean_weights, e->xadj_bits);
   KernelFn hub_fn = pick_hub_kernel(p->app, 1, e->clean_weights, e->xadj_bits);
   KernelFn tail_fn = pick_hub_kernel(p->app, 2, e->clean_weights, e->xadj_bits);
   int walk_per_sm = 0, hub_per_sm = 0, tail_per_sm = 0;
-  rc = prepare_kernel(walk_fn, smem, &walk_per_sm);
+  const size_t walk_smem = hub_walk_smem_bytes(hs.limit, p->d, a.hist_in_smem != 0);
+  rc = prepare_kernel(walk_fn, walk_smem, &walk_per_sm);
   if (!rc) rc = prepare_kernel(hub_fn, smem, &hub_per_sm);
   if (!rc) rc = prepare_kernel(tail_fn, smem, &tail_per_sm);
   if (rc) return rc;
@@ -236,13 +254,14 @@ int run_hub_batched(fw_engine* e, const fw_walk_params* p, WalkArgs a, int64_t n
   const uint32_t tail_limit = e->hub_mode == 1 ? 0u : (uint32_t)std::max<int64_t>(kHubTailMin, n / kHubTailShare);
   HubCtl* ctl = reinterpret_cast<HubCtl*>(e->d_ctl);
   FW_CUDA(cudaMemsetAsync(e->d_ctl, 0, 2 * sizeof(HubCtl), st));
-  FW_CUDA(cudaMemsetAsync(e->d_hub_cnt, 0, (size_t)e->n_hubs * 8, st));
-  a.hub.hub_ids = e->d_hub_ids; a.hub.n_hubs = e->n_hubs; a.hub.min_degree = e->hub_min_degree;
+  FW_CUDA(cudaMemsetAsync(hs.d_cnt, 0, (size_t)hs.n * 8, st));
+  a.hub.hub_ids = hs.d_ids; a.hub.n_hubs = hs.n; a.hub.min_degree = hs.limit;
   a.hub.kstate = e->d_kstate;
   a.hub.next_list = e->d_list; a.hub.bucket = e->d_bucket; a.hub.items = e->d_items;
+  a.hub.hub_parts = hs.d_parts; a.hub.best64 = e->d_best64; a.hub.part_done = e->d_part_done;
   auto parks_into = [&](int set) {
     a.hub.park_hub = e->d_park_hub[set]; a.hub.park_qi = e->d_park_qi[set];
-    a.hub.park_n = &ctl[set].park_n; a.hub.hub_cnt = e->d_hub_cnt + (size_t)set * (size_t)e->n_hubs;
+    a.hub.park_n = &ctl[set].park_n; a.hub.hub_cnt = hs.d_cnt + (size_t)set * (size_t)hs.n;
   };
   void* params[] = {&a};
   const int full_walk = e->sms * walk_per_sm, full_hub = e->sms * hub_per_sm;
@@ -253,7 +272,7 @@ int run_hub_batched(fw_engine* e, const fw_walk_params* p, WalkArgs a, int64_t n
   {
     const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
     const int grid = (int)std::min<int64_t>(full_walk, std::max<int64_t>(want, 1));
-    FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(grid), dim3(kThreads), params, smem, st));
+    FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(grid), dim3(kThreads), params, walk_smem, st));
     ++*launches;
   }
   const bool trace = getenv("FW_HUB_TRACE") != nullptr;  // development aid: the rounds on stderr
@@ -281,23 +300,24 @@ int run_hub_batched(fw_engine* e, const fw_walk_params* p, WalkArgs a, int64_t n
     if (round > (int64_t)p->d + 1) return fw::fail(FW_ERR_DEVICE, "hub batching did not come to an end (internal error)");
     const int nxt = cur ^ 1;
     FW_CUDA(cudaMemsetAsync(&ctl[nxt], 0, sizeof(HubCtl), st));
-    hub_plan_kernel<<<1, kPlanThreads, 0, st>>>(e->d_hub_cnt + (size_t)cur * (size_t)e->n_hubs, e->d_hub_base, e->d_hub_fill,
-                                                e->d_items, &ctl[cur].items_n, e->n_hubs);
+    FW_CUDA(cudaMemsetAsync(e->d_best64, 0xFF, (size_t)parked * 8, st));
+    hub_plan_kernel<<<1, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * (size_t)hs.n, hs.d_base, hs.d_fill, e->d_items,
+                                                &ctl[cur].items_n, hs.d_parts, e->d_part_done, hs.n);
     const int sgrid = (int)std::min<int64_t>(((int64_t)parked + 255) / 256, (int64_t)e->sms * 8);
-    hub_scatter_kernel<<<sgrid, 256, 0, st>>>(e->d_park_hub[cur], e->d_park_qi[cur], &ctl[cur].park_n, e->d_hub_base,
-                                              e->d_hub_fill, e->d_bucket);
+    hub_scatter_kernel<<<sgrid, 256, 0, st>>>(e->d_park_hub[cur], e->d_park_qi[cur], &ctl[cur].park_n, hs.d_base, hs.d_fill,
+                                              e->d_bucket);
     FW_CUDA(cudaGetLastError());
     // hub kernel: serves this round's batches, parks and lists for the next
     parks_into(nxt);
     a.hub.items_n = &ctl[cur].items_n; a.hub.work = &ctl[cur].work_hub; a.hub.next_n = &ctl[nxt].list_n;
     a.hub.list = nullptr; a.hub.list_n = nullptr;
-    const int64_t max_items = (int64_t)parked / 32 + e->n_hubs;
+    const int64_t max_items = ((int64_t)parked / 32) * kHubMaxParts + (int64_t)hs.parts_total;
     const int hgrid = (int)std::min<int64_t>(full_hub, std::max<int64_t>((max_items + 7) / 8, 1));
     FW_CUDA(cudaLaunchKernel((const void*)hub_fn, dim3(hgrid), dim3(kThreads), params, smem, st));
     // walk kernel: the walkers the hub kernel listed
     a.hub.list = e->d_list; a.hub.list_n = &ctl[nxt].list_n; a.hub.work = &ctl[nxt].work_walk;
     const int wgrid = (int)std::min<int64_t>(full_walk, std::max<int64_t>(((int64_t)parked + 31) / 32, 1));
-    FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(wgrid), dim3(kThreads), params, smem, st));
+    FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(wgrid), dim3(kThreads), params, walk_smem, st));
     *launches += 4;
     cur = nxt;
   }
@@ -339,10 +359,12 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   FW_CUDA(cudaEventRecord(ev_begin, st));
   // Hub batching: DeepWalk and PPR (their strip totals do not depend on the walker) with the strip
   // sampler, on graphs that have hub vertices.  Query and vertex numbers must fit 31 bits.
-  const bool hubs = e->hub_mode != 0 && e->n_hubs > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
+  // The lower hub limit when the call brings enough queries per hub to fill the batches.
+  const fw_engine::HubSet& hs = (e->hubset[1].n > 0 && n >= kHubDenseQueries * e->hubset[1].n) ? e->hubset[1] : e->hubset[0];
+  const bool hubs = e->hub_mode != 0 && hs.n > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
                     (p->app == FW_APP_DEEPWALK || p->app == FW_APP_PPR) && n < ((int64_t)1 << 31);
   if (n > 0 && hubs) {
-    const int hrc = run_hub_batched(e, p, a, n, st, smem, launches);
+    const int hrc = run_hub_batched(e, hs, p, a, n, st, smem, launches);
     if (hrc) return hrc;
   } else if (n > 0) {
     const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
@@ -423,28 +445,37 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
   const bool want_l = which == 0 ? g->label != nullptr : (which & 2) != 0;
   int rc = FW_OK;
   auto body = [&]() -> int {
-    std::vector<int64_t> hub_deg;
-    for (int64_t v = 0; v < g->V; ++v) {
-      const int64_t dg = fw::row_begin(g, v + 1) - fw::row_begin(g, v);
-      e->max_degree = std::max(e->max_degree, dg);
-      if (dg >= kHubMinDegree) hub_deg.push_back(dg);
+    for (int64_t v = 0; v < g->V; ++v)
+      e->max_degree = std::max(e->max_degree, fw::row_begin(g, v + 1) - fw::row_begin(g, v));
+    // Hubs: every vertex of at least `limit` neighbours, for both limits (the walk kernel of a
+    // hub-batched call relies on every other row fitting one stage); a graph with more than
+    // kHubMax of them runs without hub batching at that limit.
+    for (int which = 0; which < 2 && g->V < INT32_MAX; ++which) {
+      fw_engine::HubSet& hs = e->hubset[which];
+      const int64_t limit = which ? kHubLimitLow : kHubLimitHigh;
+      std::vector<int32_t> ids;
+      for (int64_t v = 0; v < g->V && (int64_t)ids.size() <= kHubMax; ++v)
+        if (fw::row_begin(g, v + 1) - fw::row_begin(g, v) >= limit) ids.push_back((int32_t)v);
+      if (ids.empty() || (int64_t)ids.size() > kHubMax) continue;
+      // rows of more than kHubPartSupers supergroups are swept by several warps, a part each
+      std::vector<uint16_t> parts(ids.size());
+      for (size_t i = 0; i < ids.size(); ++i) {
+        const int64_t b = fw::row_begin(g, ids[i]), len = fw::row_begin(g, (int64_t)ids[i] + 1) - b;
+        const int64_t nq = ((b & 3) + len + 3) >> 2, n_half = (nq + kHalfQuads - 1) / kHalfQuads, supers = (n_half + 1) >> 1;
+        parts[i] = (uint16_t)std::min<int64_t>(kHubMaxParts, (supers + kHubPartSupers - 1) / kHubPartSupers);
+        hs.parts_total += parts[i];
+      }
+      hs.n = (int32_t)ids.size();
+      hs.limit = (uint32_t)limit;
+      FW_CUDA(cudaMalloc(&hs.d_ids, ids.size() * 4));
+      FW_CUDA(cudaMemcpy(hs.d_ids, ids.data(), ids.size() * 4, cudaMemcpyHostToDevice));
+      FW_CUDA(cudaMalloc(&hs.d_cnt, ids.size() * 8));
+      FW_CUDA(cudaMalloc(&hs.d_base, ids.size() * 4));
+      FW_CUDA(cudaMalloc(&hs.d_fill, ids.size() * 4));
+      FW_CUDA(cudaMalloc(&hs.d_parts, parts.size() * 2));
+      FW_CUDA(cudaMemcpy(hs.d_parts, parts.data(), parts.size() * 2, cudaMemcpyHostToDevice));
     }
-    // hubs: every vertex of at least kHubMinDegree neighbours (the walk kernel of a hub-batched call
-    // relies on every other row fitting one 4 KB stage); a graph with more than kHubMax of them
-    // runs without hub batching
-    const int64_t hub_t = kHubMinDegree;
-    std::vector<int32_t> hub_ids;
-    if (!hub_deg.empty() && (int64_t)hub_deg.size() <= kHubMax && g->V < INT32_MAX)
-      for (int64_t v = 0; v < g->V; ++v)
-        if (fw::row_begin(g, v + 1) - fw::row_begin(g, v) >= hub_t) hub_ids.push_back((int32_t)v);
-    if (!hub_ids.empty() && hub_t < ((int64_t)1 << 31)) {
-      e->n_hubs = (int32_t)hub_ids.size();
-      e->hub_min_degree = (uint32_t)hub_t;
-      FW_CUDA(cudaMalloc(&e->d_hub_ids, hub_ids.size() * 4));
-      FW_CUDA(cudaMemcpy(e->d_hub_ids, hub_ids.data(), hub_ids.size() * 4, cudaMemcpyHostToDevice));
-      FW_CUDA(cudaMalloc(&e->d_hub_cnt, hub_ids.size() * 8));
-      FW_CUDA(cudaMalloc(&e->d_hub_base, hub_ids.size() * 4));
-      FW_CUDA(cudaMalloc(&e->d_hub_fill, hub_ids.size() * 4));
+    if (e->hubset[0].n > 0 || e->hubset[1].n > 0) {
       FW_CUDA(cudaMalloc(&e->d_ctl, 2 * sizeof(HubCtl)));
       FW_CUDA(cudaMallocHost(&e->h_ctl, 64));
     }
@@ -479,9 +510,11 @@ extern "C" void fw_engine_destroy(fw_engine* e) {
   cudaFree(e->d_xadj); cudaFree(e->d_adj); cudaFree(e->d_weight); cudaFree(e->d_label);
   cudaFree(e->d_scratch);
   if (e->h_scratch) cudaFreeHost(e->h_scratch);
-  cudaFree(e->d_hub_ids); cudaFree(e->d_hub_cnt); cudaFree(e->d_hub_base); cudaFree(e->d_hub_fill); cudaFree(e->d_ctl);
+  for (auto& hs : e->hubset) { cudaFree(hs.d_ids); cudaFree(hs.d_cnt); cudaFree(hs.d_base); cudaFree(hs.d_fill); cudaFree(hs.d_parts); }
+  cudaFree(e->d_ctl);
   if (e->h_ctl) cudaFreeHost(e->h_ctl);
   cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
+  cudaFree(e->d_best64); cudaFree(e->d_part_done);
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_park_hub[i]); cudaFree(e->d_park_qi[i]); }
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_starts[i]); cudaFree(e->d_result[i]); }
   if (e->stream) cudaStreamDestroy(e->stream);
@@ -502,10 +535,10 @@ extern "C" int fw_engine_set_hub_batching(fw_engine* e, int mode) {
   return FW_OK;
 }
 
-extern "C" int fw_engine_hubs(const fw_engine* e, int32_t* n_hubs, uint32_t* min_degree) {
-  if (!e) return fw::fail(FW_ERR_ARG, "fw_engine_hubs: null engine");
-  if (n_hubs) *n_hubs = e->n_hubs;
-  if (min_degree) *min_degree = e->hub_min_degree;
+extern "C" int fw_engine_hubs(const fw_engine* e, int which, int32_t* n_hubs, uint32_t* min_degree) {
+  if (!e || which < 0 || which > 1) return fw::fail(FW_ERR_ARG, "fw_engine_hubs: null engine or which not 0 / 1");
+  if (n_hubs) *n_hubs = e->hubset[which].n;
+  if (min_degree) *min_degree = which ? kHubLimitLow : kHubLimitHigh;
   return FW_OK;
 }
 

@@ -154,14 +154,17 @@ int fw_engine_device(const fw_engine* e, int* device, int* sm_count);
 int fw_engine_set_sharing(fw_engine* e, int mode);
 /* Hub batching (the other half of the role of sampler_block, include/sampler.cuh:87-127, and of
  * the degree-binned dispatch of include/walker.cuh:1357-1419): walkers that arrive at a vertex of
- * 1,024 or more neighbours wait there, and one sweep of the hub's row serves up to 32 of them.
+ * about a thousand neighbours or more (1,016; 504 in calls with many queries per such vertex)
+ * wait there, and one sweep of the hub's row serves up to 32 of them.
  * DeepWalk and PPR with the strip sampler; a walk call then is a series of kernel launches.
  * mode -1 (default): on when the graph has such vertices, and the last few parked walkers of a call
  * are walked to the end by one launch without batching; 0: off; 1: on, batching to the last walker.
  * Results do not depend on it. */
 int fw_engine_set_hub_batching(fw_engine* e, int mode);
-/* Number of hub vertices of the engine's graph and the row length from which a vertex is one. */
-int fw_engine_hubs(const fw_engine* e, int32_t* n_hubs, uint32_t* min_degree);
+/* Number of hub vertices of the engine's graph and the row length from which a vertex is one,
+ * for the two limits a call chooses from (which = 0: 1,016 neighbours, 1: 504; the lower one
+ * serves calls that bring at least a hundred queries per hub). */
+int fw_engine_hubs(const fw_engine* e, int which, int32_t* n_hubs, uint32_t* min_degree);
 
 /*
  * walk_test (include/walker.cuh:49-52, src/walk.cu:527-574): start points on
