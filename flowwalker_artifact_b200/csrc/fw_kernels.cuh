@@ -73,6 +73,8 @@ constexpr int kSlotSteps = 0, kSlotScanned = 1, kSlotStatus = 2, kSlotCounter = 
 struct HubArgs {
   const int32_t* hub_ids;   // the hub vertices, ascending; a vertex is a hub iff its row has >= min_degree edges
   int32_t n_hubs;
+  int32_t classes;          // walkers of a hub that may share a sweep: 1, or MetaPath's schema length (those at
+                            // the same step modulo it want the same label); a batch is keyed hub * classes + class
   uint32_t min_degree;
   int32_t* kstate;          // steps taken so far by every query that is parked or listed
   const int32_t* list;      // walk kernel: queries to resume (nullptr: fresh queries 0 .. n-1)
@@ -1418,7 +1420,7 @@ __device__ __forceinline__ int32_t hub_index(const int32_t* __restrict__ ids, in
 
 // A walker that arrived at a hub vertex `cur` after k steps waits there for the next hub launch.
 __device__ __forceinline__ void hub_park(const HubArgs& hb, long long qi, int32_t k, int32_t cur) {
-  const int32_t h = hub_index(hb.hub_ids, hb.n_hubs, cur);
+  const int32_t h = hub_index(hb.hub_ids, hb.n_hubs, cur) * hb.classes + (hb.classes > 1 ? k % hb.classes : 0);
   const uint32_t pos = atomicAdd(hb.park_n, 1u);
   hb.park_hub[pos] = h;
   hb.park_qi[pos] = (int32_t)qi;
@@ -1573,7 +1575,8 @@ __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, Of
           c.head = (uint32_t)(b - 4 * q0);
           c.tail = c.head + len;
           c.nq = (c.tail + 3u) >> 2;
-          c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = nullptr;
+          c.prev = -1; c.prow = a.adj; c.plen = 0u; c.from = 0u; c.flags = nullptr;
+          c.want = APP == FW_APP_METAPATH ? a.schema[ks % (uint32_t)a.schema_len] : 0;
         };
         int s = __ffs((int)m) - 1;
         m &= m - 1u;
@@ -1807,7 +1810,7 @@ __host__ __device__ constexpr uint32_t hub_part_supers(uint32_t supers, uint32_t
 
 template <int APP, bool CLEAN, typename OffT>
 __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __grid_constant__ WalkArgs a) {
-  static_assert(APP == FW_APP_DEEPWALK || APP == FW_APP_PPR, "strip totals must not depend on the walker");
+  static_assert(APP != FW_APP_NODE2VEC, "strip totals must not depend on the walker (MetaPath: batches are per wanted label)");
   extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][2];
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -1830,7 +1833,7 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
 
   const OffT* __restrict__ xadj = static_cast<const OffT*>(a.xadj);
   const int64_t D = (int64_t)a.d + 1;
-  const int4* const prim_base = reinterpret_cast<const int4*>(a.weight);
+  const int4* const prim_base = reinterpret_cast<const int4*>(APP == FW_APP_METAPATH ? (const void*)a.label : (const void*)a.weight);
   const int4* const lane_ptr = reinterpret_cast<const int4*>(ring_ptr) + lane;
   const uint32_t n_items = *a.hub.items_n;
   unsigned long long my_steps = 0, my_scanned = 0;
@@ -1843,7 +1846,7 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
     if (item >= (unsigned long long)n_items) break;
     const int4 it = __ldg(a.hub.items + item);  // hub index, first entry, entries | part << 8 | parts << 16, group
     const uint32_t n_in = (uint32_t)it.z & 0xFFu, part = ((uint32_t)it.z >> 8) & 0xFFu, parts = (uint32_t)it.z >> 16;
-    const int32_t v = __ldg(a.hub.hub_ids + it.x);
+    const int32_t v = __ldg(a.hub.hub_ids + it.x / a.hub.classes);
     const int64_t b = (int64_t)__ldg(xadj + v);
     const uint32_t len = (uint32_t)((int64_t)__ldg(xadj + v + 1) - b);
     const int64_t q0 = b >> 2;
@@ -1853,7 +1856,8 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
     c.head = (uint32_t)(b - 4 * q0);
     c.tail = c.head + len;
     c.nq = (c.tail + 3u) >> 2;
-    c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = nullptr;
+    c.prev = -1; c.prow = a.adj; c.plen = 0u; c.from = 0u; c.flags = nullptr;
+    c.want = APP == FW_APP_METAPATH ? a.schema[it.x % a.hub.classes] : 0;  // the label every walker of the batch wants
     // the walker this lane stands for
     const bool have = lane < n_in;
     const long long qi = have ? (long long)__ldg(a.hub.bucket + it.y + lane) : 0;
@@ -2000,12 +2004,13 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
   }
 }
 
-// Groups the parked walkers by hub: exclusive scan of the per-hub counts into `base`, one batch item
-// per 32 walkers of a hub, the counts and the scatter cursors back to zero.  One CTA of kPlanThreads.
+// Groups the parked walkers by hub (n_hubs counts the hub-and-class keys): exclusive scan of the
+// per-key counts into `base`, one batch item per 32 walkers of a key and part of the hub's row, the
+// counts and the scatter cursors back to zero.  One CTA of kPlanThreads.
 constexpr int kPlanThreads = 1024;
 __global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, uint32_t* base, uint32_t* fill, int4* items,
                                                                 uint32_t* items_n, const uint16_t* __restrict__ parts,
-                                                                uint32_t* part_done, int n_hubs) {
+                                                                uint32_t* part_done, int n_hubs, int classes) {
   __shared__ uint32_t s_cnt[kPlanThreads], s_bat[kPlanThreads];
   const int t = threadIdx.x;
   const int per = (n_hubs + kPlanThreads - 1) / kPlanThreads;
@@ -2013,7 +2018,7 @@ __global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, u
   uint32_t my_cnt = 0, my_bat = 0;
   for (int h = h0; h < h1; ++h) {
     my_cnt += cnt[h];
-    my_bat += ((cnt[h] + 31u) >> 5) * parts[h];
+    my_bat += ((cnt[h] + 31u) >> 5) * parts[h / classes];
   }
   s_cnt[t] = my_cnt;
   s_bat[t] = my_bat;
@@ -2027,7 +2032,7 @@ __global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, u
   }
   uint32_t at = s_cnt[t] - my_cnt, ib = s_bat[t] - my_bat;
   for (int h = h0; h < h1; ++h) {
-    const uint32_t n = cnt[h], np = parts[h];
+    const uint32_t n = cnt[h], np = parts[h / classes];
     base[h] = at;
     for (uint32_t off = 0; off < n; off += 32u) {
       const uint32_t group = ib;
@@ -2076,6 +2081,7 @@ inline KernelFn pick_hub_kernel_of(int which, bool clean, int xadj_bits) {
 }
 inline KernelFn pick_hub_kernel(int app, int which, bool clean, int xadj_bits) {
   if (app == FW_APP_PPR) return pick_hub_kernel_of<FW_APP_PPR>(which, clean, xadj_bits);
+  if (app == FW_APP_METAPATH) return pick_hub_kernel_of<FW_APP_METAPATH>(which, true, xadj_bits);  // 0/1 biases: nothing to clamp
   return pick_hub_kernel_of<FW_APP_DEEPWALK>(which, clean, xadj_bits);
 }
 

@@ -87,9 +87,10 @@ struct fw_engine {
     int32_t n = 0;
     uint32_t limit = 0;            // a vertex is a hub iff its row has at least this many edges
     int32_t* d_ids = nullptr;      // ascending
-    uint32_t* d_cnt = nullptr;     // [2][n] parked walkers per hub, this round and the next
-    uint32_t* d_base = nullptr;    // [n]
-    uint32_t* d_fill = nullptr;    // [n]
+    uint32_t* d_cnt = nullptr;     // [2][n * classes] parked walkers per hub and class, this round and the next
+    uint32_t* d_base = nullptr;    // [n * classes]
+    uint32_t* d_fill = nullptr;    // [n * classes]
+    int classes_cap = 0;           // classes the three arrays above are sized for
     uint16_t* d_parts = nullptr;   // [n] parts the sweep of a hub's row is split into
     uint64_t parts_total = 0;      // their sum
   } hubset[2];                     // 0: limit 1,016, 1: limit 504
@@ -207,8 +208,10 @@ int prepare_kernel(KernelFn fn, size_t smem, int* per_sm) {
 
 // Enqueues: scratch reset, kernel between ev[0] and ev[1], scratch read-back.
 // Buffers of a hub-batched call for n queries.
-int ensure_hub_buffers(fw_engine* e, size_t n) {
-  if (n <= e->hub_cap) return FW_OK;
+int ensure_hub_buffers(fw_engine* e, size_t n, size_t classes) {
+  const size_t parts_total = (size_t)std::max(e->hubset[0].parts_total, e->hubset[1].parts_total) * classes;
+  if (n <= e->hub_cap && (e->hub_cap / 32) * (size_t)kHubMaxParts + parts_total + 1 <= e->items_cap) return FW_OK;
+  n = std::max(n, e->hub_cap);
   cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
   cudaFree(e->d_best64); cudaFree(e->d_part_done);
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_park_hub[i]); cudaFree(e->d_park_qi[i]); }
@@ -225,7 +228,7 @@ int ensure_hub_buffers(fw_engine* e, size_t n) {
     FW_CUDA(cudaMalloc(&e->d_park_qi[i], cap * 4));
   }
   // every hub has at most one batch that is not full, every batch one item per part of the row
-  e->items_cap = (cap / 32) * (size_t)kHubMaxParts + (size_t)std::max(e->hubset[0].parts_total, e->hubset[1].parts_total) + 1;
+  e->items_cap = (cap / 32) * (size_t)kHubMaxParts + parts_total + 1;
   FW_CUDA(cudaMalloc(&e->d_items, e->items_cap * sizeof(int4)));
   FW_CUDA(cudaMalloc(&e->d_part_done, e->items_cap * 4));
   FW_CUDA(cudaMalloc(&e->d_best64, cap * 8));
@@ -236,10 +239,22 @@ int ensure_hub_buffers(fw_engine* e, size_t n) {
 // The launches of a hub-batched call (see hub_kernel): the walk kernel on the fresh queries, then
 // rounds of plan, scatter, hub kernel, walk kernel while walkers are parked at hubs.  Every round
 // ends with the host reading the number of parked walkers, so this returns with the walk done.
-int run_hub_batched(fw_engine* e, const fw_engine::HubSet& hs, const fw_walk_params* p, WalkArgs a, int64_t n,
+int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p, WalkArgs a, int64_t n,
                     cudaStream_t st, size_t smem, int* launches) {
-  int rc = ensure_hub_buffers(e, (size_t)n);
+  // MetaPath: walkers at the same step modulo the schema length want the same label and may share a sweep
+  const int classes = p->app == FW_APP_METAPATH ? p->schema_len : 1;
+  const size_t keys = (size_t)hs.n * (size_t)classes;
+  int rc = ensure_hub_buffers(e, (size_t)n, (size_t)classes);
   if (rc) return rc;
+  if (classes > hs.classes_cap) {
+    cudaFree(hs.d_cnt); cudaFree(hs.d_base); cudaFree(hs.d_fill);
+    hs.d_cnt = hs.d_base = hs.d_fill = nullptr;
+    hs.classes_cap = 0;
+    FW_CUDA(cudaMalloc(&hs.d_cnt, keys * 8));
+    FW_CUDA(cudaMalloc(&hs.d_base, keys * 4));
+    FW_CUDA(cudaMalloc(&hs.d_fill, keys * 4));
+    hs.classes_cap = classes;
+  }
   KernelFn walk_fn = pick_hub_kernel(p->app, hs.limit == kHubLimitLow ? 3 : 0, e->clean_weights, e->xadj_bits);
   KernelFn hub_fn = pick_hub_kernel(p->app, 1, e->clean_weights, e->xadj_bits);
   KernelFn tail_fn = pick_hub_kernel(p->app, 2, e->clean_weights, e->xadj_bits);
@@ -254,14 +269,14 @@ int run_hub_batched(fw_engine* e, const fw_engine::HubSet& hs, const fw_walk_par
   const uint32_t tail_limit = e->hub_mode == 1 ? 0u : (uint32_t)std::max<int64_t>(kHubTailMin, n / kHubTailShare);
   HubCtl* ctl = reinterpret_cast<HubCtl*>(e->d_ctl);
   FW_CUDA(cudaMemsetAsync(e->d_ctl, 0, 2 * sizeof(HubCtl), st));
-  FW_CUDA(cudaMemsetAsync(hs.d_cnt, 0, (size_t)hs.n * 8, st));
-  a.hub.hub_ids = hs.d_ids; a.hub.n_hubs = hs.n; a.hub.min_degree = hs.limit;
+  FW_CUDA(cudaMemsetAsync(hs.d_cnt, 0, keys * 8, st));
+  a.hub.hub_ids = hs.d_ids; a.hub.n_hubs = hs.n; a.hub.min_degree = hs.limit; a.hub.classes = classes;
   a.hub.kstate = e->d_kstate;
   a.hub.next_list = e->d_list; a.hub.bucket = e->d_bucket; a.hub.items = e->d_items;
   a.hub.hub_parts = hs.d_parts; a.hub.best64 = e->d_best64; a.hub.part_done = e->d_part_done;
   auto parks_into = [&](int set) {
     a.hub.park_hub = e->d_park_hub[set]; a.hub.park_qi = e->d_park_qi[set];
-    a.hub.park_n = &ctl[set].park_n; a.hub.hub_cnt = hs.d_cnt + (size_t)set * (size_t)hs.n;
+    a.hub.park_n = &ctl[set].park_n; a.hub.hub_cnt = hs.d_cnt + (size_t)set * keys;
   };
   void* params[] = {&a};
   const int full_walk = e->sms * walk_per_sm, full_hub = e->sms * hub_per_sm;
@@ -301,8 +316,8 @@ int run_hub_batched(fw_engine* e, const fw_engine::HubSet& hs, const fw_walk_par
     const int nxt = cur ^ 1;
     FW_CUDA(cudaMemsetAsync(&ctl[nxt], 0, sizeof(HubCtl), st));
     FW_CUDA(cudaMemsetAsync(e->d_best64, 0xFF, (size_t)parked * 8, st));
-    hub_plan_kernel<<<1, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * (size_t)hs.n, hs.d_base, hs.d_fill, e->d_items,
-                                                &ctl[cur].items_n, hs.d_parts, e->d_part_done, hs.n);
+    hub_plan_kernel<<<1, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, hs.d_base, hs.d_fill, e->d_items,
+                                                &ctl[cur].items_n, hs.d_parts, e->d_part_done, (int)keys, classes);
     const int sgrid = (int)std::min<int64_t>(((int64_t)parked + 255) / 256, (int64_t)e->sms * 8);
     hub_scatter_kernel<<<sgrid, 256, 0, st>>>(e->d_park_hub[cur], e->d_park_qi[cur], &ctl[cur].park_n, hs.d_base, hs.d_fill,
                                               e->d_bucket);
@@ -311,7 +326,7 @@ int run_hub_batched(fw_engine* e, const fw_engine::HubSet& hs, const fw_walk_par
     parks_into(nxt);
     a.hub.items_n = &ctl[cur].items_n; a.hub.work = &ctl[cur].work_hub; a.hub.next_n = &ctl[nxt].list_n;
     a.hub.list = nullptr; a.hub.list_n = nullptr;
-    const int64_t max_items = ((int64_t)parked / 32) * kHubMaxParts + (int64_t)hs.parts_total;
+    const int64_t max_items = ((int64_t)parked / 32) * kHubMaxParts + (int64_t)hs.parts_total * classes;
     const int hgrid = (int)std::min<int64_t>(full_hub, std::max<int64_t>((max_items + 7) / 8, 1));
     FW_CUDA(cudaLaunchKernel((const void*)hub_fn, dim3(hgrid), dim3(kThreads), params, smem, st));
     // walk kernel: the walkers the hub kernel listed
@@ -357,12 +372,15 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   const size_t words = (size_t)kSlotHist + (size_t)p->d + 1;
   FW_CUDA(cudaMemsetAsync(d_scratch, 0, words * 8, st));
   FW_CUDA(cudaEventRecord(ev_begin, st));
-  // Hub batching: DeepWalk and PPR (their strip totals do not depend on the walker) with the strip
-  // sampler, on graphs that have hub vertices.  Query and vertex numbers must fit 31 bits.
+  // Hub batching: DeepWalk, PPR and MetaPath (the strip totals of a row do not depend on the walker,
+  // for MetaPath on the label it wants) with the strip sampler, on graphs that have hub vertices.
+  // Query and vertex numbers must fit 31 bits.
   // The lower hub limit when the call brings enough queries per hub to fill the batches.
-  const fw_engine::HubSet& hs = (e->hubset[1].n > 0 && n >= kHubDenseQueries * e->hubset[1].n) ? e->hubset[1] : e->hubset[0];
+  fw_engine::HubSet& hs = (e->hubset[1].n > 0 && n >= kHubDenseQueries * e->hubset[1].n) ? e->hubset[1] : e->hubset[0];
+  // (node2vec's strip totals depend on the walker's previous vertex: no batching)
   const bool hubs = e->hub_mode != 0 && hs.n > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
-                    (p->app == FW_APP_DEEPWALK || p->app == FW_APP_PPR) && n < ((int64_t)1 << 31);
+                    p->app != FW_APP_NODE2VEC && n < ((int64_t)1 << 31) &&
+                    (int64_t)hs.n * (p->app == FW_APP_METAPATH ? p->schema_len : 1) < ((int64_t)1 << 30);
   if (n > 0 && hubs) {
     const int hrc = run_hub_batched(e, hs, p, a, n, st, smem, launches);
     if (hrc) return hrc;
@@ -469,9 +487,6 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
       hs.limit = (uint32_t)limit;
       FW_CUDA(cudaMalloc(&hs.d_ids, ids.size() * 4));
       FW_CUDA(cudaMemcpy(hs.d_ids, ids.data(), ids.size() * 4, cudaMemcpyHostToDevice));
-      FW_CUDA(cudaMalloc(&hs.d_cnt, ids.size() * 8));
-      FW_CUDA(cudaMalloc(&hs.d_base, ids.size() * 4));
-      FW_CUDA(cudaMalloc(&hs.d_fill, ids.size() * 4));
       FW_CUDA(cudaMalloc(&hs.d_parts, parts.size() * 2));
       FW_CUDA(cudaMemcpy(hs.d_parts, parts.data(), parts.size() * 2, cudaMemcpyHostToDevice));
     }

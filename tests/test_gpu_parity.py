@@ -98,7 +98,7 @@ def test_star_hub_shared_between_warps(app, kw, n):
 
 
 @pytest.mark.parametrize("hub", [0, -1, 1])
-@pytest.mark.parametrize("app,kw", APPS[:2])
+@pytest.mark.parametrize("app,kw", APPS[:2] + [APPS[3], (fw.APP_METAPATH, dict(d=7, schema=[3, 3, 0]))])
 def test_hub_batching_on_and_off(app, kw, hub):
     """Walkers that meet at a vertex of 1,024 or more neighbours share one sweep of its row (a walk
     call is then a series of launches); with it switched off every walker sweeps for itself in one
@@ -109,11 +109,12 @@ def test_hub_batching_on_and_off(app, kw, hub):
     arrs = graphs.ragged(np.int64 if app == fw.APP_PPR else np.uint32)
     starts = np.concatenate([np.arange(arrs["n_rows"])] * 3).astype(np.int32)
     kw2 = dict(kw)
-    kw2["d"] = 15
+    kw2["d"] = 15 if app != fw.APP_METAPATH else kw["d"]
     out = run_both(arrs, app, kw2, starts, fw.GROUP_STRIP, seed=21, base=7, hub=hub)
     assert_same(out)
     assert (out[1].launches == 1) == (hub == 0)
     star = graphs.star()
+    star["label"][:100000] = np.arange(100000) % 5
     starts = np.zeros(3000, dtype=np.int32)
     starts[1::3] = np.arange(1, 3000, 3) % 1000 + 1
     out = run_both(star, app, kw2, starts, fw.GROUP_STRIP, seed=22, hub=hub)
