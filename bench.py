@@ -60,7 +60,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-strong", action="store_true", help="skip the partitioned-job legs of a multi-GPU run")
     ap.add_argument("--no-numa", action="store_true", help="leave the rank's CPU affinity as it is")
-    ap.add_argument("--e2e-batches", type=int, default=8, help="double-buffered batches of the end-to-end leg")
+    ap.add_argument("--e2e-batches", type=int, default=1, help="double-buffered batches of the end-to-end leg")
     return ap.parse_args()
 
 

@@ -1501,6 +1501,63 @@ __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, Of
   unsigned long long* const work = HUBS != kHubOff ? a.hub.work : a.scratch + kSlotCounter;
   const long long n_work = (HUBS != kHubOff && a.hub.list != nullptr) ? (long long)*a.hub.list_n : (long long)a.n;
   FW_PROF(unsigned long long prof_t[3] = {0, 0, 0}, prof_n[3] = {0, 0, 0}, prof_sub = 0; const long long prof_begin = clock64();)
+  if constexpr (kSlots == 1 && HUBS == kHubOff) {
+    // One query per warp, walked to its end with all state in uniform registers (node2vec: its
+    // kernels are the largest, and the slot bookkeeping below cost them a third of their speed).
+    while (!ring.failed) {
+      long long first = 0;
+      if (lane == 0) first = (long long)atomicAdd(work, (unsigned long long)kMinClaim);
+      first = __shfl_sync(0xFFFFFFFFu, first, 0);
+      if (first >= n_work) break;
+      const long long stop = first + kMinClaim < n_work ? first + kMinClaim : n_work;
+      for (long long q1 = first; q1 < stop && !ring.failed; ++q1) {
+        const uint64_t qid = a.qid_base + (uint64_t)q1 * a.qid_stride;
+        const uint32_t ql = (uint32_t)qid, qh = (uint32_t)(qid >> 32);
+        int32_t* __restrict__ row_out = a.result + q1 * D;
+        int32_t at = __ldg(a.starts + q1);
+        if (lane == 0) row_out[0] = at;
+        StepCtx c;
+        c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u;
+        c.flags = &s_flags[APP == FW_APP_NODE2VEC ? warp : 0][0];
+        int kk = 0;
+        if (at < 0 || (int64_t)at >= a.V) {
+          status |= FW_STATUS_BAD_START;
+        } else {
+          while (kk < a.d) {
+            const int64_t b = (int64_t)__ldg(xadj + at), e = (int64_t)__ldg(xadj + at + 1);
+            if (e <= b) break;
+            const int64_t q0 = b >> 2;
+            c.prim = prim_base + q0;
+            c.sec = sec_base + q0;
+            c.nq = (uint32_t)(((e + 3) >> 2) - q0);
+            c.head = (uint32_t)(b - 4 * q0);
+            c.tail = (uint32_t)(e - 4 * q0);
+            if (APP == FW_APP_METAPATH) c.want = a.schema[kk % a.schema_len];
+            c.from = 0u;
+            const uint32_t rel = sample_row_warp<APP, MODE, CLEAN>(a, c, (uint32_t)kk, ql, qh, lane, ring, ring_ptr, &s_task);
+            if (rel == 0xFFFFFFFFu) break;  // include/walker.cuh:1373-1374 (or a failed wait)
+            const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
+            if (nxt < 0 || (int64_t)nxt >= a.V) { status |= FW_STATUS_BAD_NEIGHBOR; break; }
+            if (lane == 0) row_out[kk + 1] = nxt;  // include/walker.cuh:1380-1381
+            my_scanned += (unsigned long long)(e - b);
+            c.prev = at; c.prow = a.adj + b; c.plen = (uint32_t)(e - b);  // include/gpu_task.cuh:70-77
+            at = nxt;
+            ++kk;
+            if (APP == FW_APP_PPR) {  // include/app.cuh:88-94
+              const fw::Philox4 r = fw::philox4x32_10(0u, (uint32_t)(kk - 1) | (fw::kPurposeStop << 28), ql, qh, a.rk);
+              if (r.x < a.tp_thresh) break;
+            }
+          }
+        }
+        for (int z = kk + 1 + (int)lane; z <= a.d; z += 32) row_out[z] = -1;
+        my_steps += (unsigned long long)kk;
+        if (lane == 0) {
+          if (a.hist_in_smem) atomicAdd(&s_hist[kk], 1u);
+          else atomicAdd(a.scratch + kSlotHist + kk, 1ull);
+        }
+      }
+    }
+  } else
   while (!ring.failed) {
     // ---- hand queries to the empty slots ----
     const uint32_t empty = __ballot_sync(0xFFFFFFFFu, slot_lane && st == 0u);
@@ -2011,40 +2068,52 @@ constexpr int kPlanThreads = 1024;
 __global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, uint32_t* base, uint32_t* fill, int4* items,
                                                                 uint32_t* items_n, const uint16_t* __restrict__ parts,
                                                                 uint32_t* part_done, int n_hubs, int classes) {
-  __shared__ uint32_t s_cnt[kPlanThreads], s_bat[kPlanThreads];
-  const int t = threadIdx.x;
-  const int per = (n_hubs + kPlanThreads - 1) / kPlanThreads;
-  const int h0 = min(t * per, n_hubs), h1 = min(h0 + per, n_hubs);
-  uint32_t my_cnt = 0, my_bat = 0;
-  for (int h = h0; h < h1; ++h) {
-    my_cnt += cnt[h];
-    my_bat += ((cnt[h] + 31u) >> 5) * parts[h / classes];
-  }
-  s_cnt[t] = my_cnt;
-  s_bat[t] = my_bat;
-  __syncthreads();
-  for (int off = 1; off < kPlanThreads; off <<= 1) {  // inclusive scan of both
-    const uint32_t x = t >= off ? s_cnt[t - off] : 0u, y = t >= off ? s_bat[t - off] : 0u;
-    __syncthreads();
-    s_cnt[t] += x;
-    s_bat[t] += y;
-    __syncthreads();
-  }
-  uint32_t at = s_cnt[t] - my_cnt, ib = s_bat[t] - my_bat;
-  for (int h = h0; h < h1; ++h) {
-    const uint32_t n = cnt[h], np = parts[h / classes];
-    base[h] = at;
-    for (uint32_t off = 0; off < n; off += 32u) {
-      const uint32_t group = ib;
-      part_done[group] = 0u;
-      for (uint32_t p = 0; p < np; ++p)
-        items[ib++] = make_int4(h, (int)(at + off), (int)(min(32u, n - off) | (p << 8) | (np << 16)), (int)group);
+  __shared__ uint32_t s_wc[32], s_wb[32], s_tot[2];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  uint32_t carry_c = 0, carry_b = 0;  // walkers and items before this tile
+  for (int tile = 0; tile < n_hubs; tile += kPlanThreads) {  // one key per thread: coalesced, scanned by shuffles
+    const int h = tile + t;
+    const uint32_t n = h < n_hubs ? cnt[h] : 0u, np = h < n_hubs ? parts[h / classes] : 0u;
+    const uint32_t nb = ((n + 31u) >> 5) * np;
+    uint32_t ic = n, ib = nb;  // inclusive scans over the warp
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, ic, off), y = __shfl_up_sync(0xFFFFFFFFu, ib, off);
+      if (lane >= off) { ic += x; ib += y; }
     }
-    at += n;
-    cnt[h] = 0u;
-    fill[h] = 0u;
+    if (lane == 31) { s_wc[warp] = ic; s_wb[warp] = ib; }
+    __syncthreads();
+    if (warp == 0) {  // the warps' totals -> their exclusive offsets, and the tile's totals
+      const uint32_t wc = s_wc[lane], wb = s_wb[lane];
+      uint32_t xc = wc, xb = wb;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, xc, off), y = __shfl_up_sync(0xFFFFFFFFu, xb, off);
+        if (lane >= off) { xc += x; xb += y; }
+      }
+      s_wc[lane] = xc - wc;
+      s_wb[lane] = xb - wb;
+      if (lane == 31) { s_tot[0] = xc; s_tot[1] = xb; }
+    }
+    __syncthreads();
+    if (h < n_hubs) {
+      const uint32_t at = carry_c + s_wc[warp] + ic - n;
+      uint32_t it = carry_b + s_wb[warp] + ib - nb;
+      base[h] = at;
+      for (uint32_t off = 0; off < n; off += 32u) {
+        const uint32_t group = it;
+        part_done[group] = 0u;
+        for (uint32_t p = 0; p < np; ++p)
+          items[it++] = make_int4(h, (int)(at + off), (int)(min(32u, n - off) | (p << 8) | (np << 16)), (int)group);
+      }
+      if (n != 0u) cnt[h] = 0u;
+      fill[h] = 0u;
+    }
+    carry_c += s_tot[0];
+    carry_b += s_tot[1];
+    __syncthreads();
   }
-  if (t == kPlanThreads - 1) *items_n = s_bat[t];
+  if (t == 0) *items_n = carry_b;
 }
 
 __global__ void hub_scatter_kernel(const int32_t* __restrict__ park_hub, const int32_t* __restrict__ park_qi,
