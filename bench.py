@@ -11,8 +11,11 @@ carries the barrier and the final reduction of counters and times.
 
 Prints ONE JSON line (rank 0).  `value` is walk steps per second with inputs
 resident in HBM; `e2e` is the same through fw_walk_batch_into with pinned host buffers
-(start vertices copied in, the whole walk table copied out, eight double-buffered batches:
-measured 105.5 / 103.8 / 104.2 / 108.3 ms per pass with 4 / 8 / 16 / 32 batches).
+(start vertices copied in, the whole walk table copied out).  A pass of this workload is a
+hub-batched call: a series of kernel launches in which walkers that meet at a hub vertex share
+one sweep of its row, so the walk of a pass is best done in one piece (measured 85.6 / 92.8 /
+101.6 / 110.9 ms per end-to-end pass as 1 / 2 / 3 / 4 double-buffered batches: every batch
+pays the fixed cost of its own series) and `--e2e-batches` defaults to 1.
 
 With N > 1 the line also carries `strong`: ONE job partitioned over the ranks, the way a
 user shards queries over the GPUs of a box -- rank r of R takes the contiguous id range
@@ -122,17 +125,15 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-# Counters of the walk kernel that only a profiler sees, per workload (app, scale, edge factor, d,
-# group mode): DRAM bytes per algorithmic byte (dram__bytes_read.sum + dram__bytes_write.sum of an
-# `ncu` capture of a launch of the same kernel on the same graph with fewer queries, over that
-# launch's algorithmic bytes; both grow in proportion with the number of queries), the share of
-# issue slots in use and the L2 hit rate.  Each entry names the kernel revision
-# (fw_kernel_revision) it was captured on; a line measured on another revision, or on a workload
-# without an entry, reports traffic = null with the reason.
+# Counters of the walk that only a profiler sees, per workload (app, scale, edge factor, d, group
+# mode): DRAM bytes per algorithmic byte (dram__bytes_read.sum + dram__bytes_write.sum over every
+# walk and hub kernel launch of an `ncu` capture of the same call with fewer queries on the same
+# graph, over that call's algorithmic bytes; both grow in proportion with the number of queries as
+# long as the call uses the same hub limit), the share of issue slots in use and the L2 hit rate
+# (time-weighted over the launches).  Each entry names the kernel revision (fw_kernel_revision) it
+# was captured on; a line measured on another revision, or on a workload without an entry, reports
+# traffic = null with the reason.
 PROFILED = {
-    ("deepwalk", 22, 16, 80, 64): {
-        "kernel_revision": "ring2k-1q", "captured_on": "1,000,000-query launch of the same graph",
-        "dram_per_algorithmic_byte": 0.2131, "issue_active": 0.856, "l2_hit_rate": 0.698},
 }
 
 
@@ -541,9 +542,16 @@ def main():
         achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9
         rev = fw.lib().fw_kernel_revision().decode()
         prof = PROFILED.get((args.app, args.scale, args.edge_factor, args.d, args.group or 64))
+        per_pass_launches = dev["launches"] / launches
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_source": peak_kind + " copy bandwidth", "kernel": "walk_kernel", "kernel_revision": rev,
-                "algorithmic_bytes_per_launch": per_launch_bytes, "kernel_ms_per_launch": per_launch_ms}
+                "peak_source": peak_kind + " copy bandwidth",
+                "kernel": "walk_kernel" if per_pass_launches == 1 else
+                          "walk_kernel + hub_kernel: a hub-batched pass is a series of launches (%.0f per pass, plan and "
+                          "scatter kernels included); bytes and time are those of the whole pass" % per_pass_launches,
+                "kernel_revision": rev, "launches_per_pass": per_pass_launches,
+                "algorithmic_bytes_per_launch": per_launch_bytes, "kernel_ms_per_launch": per_launch_ms,
+                "algorithmic_bytes": "4 B per neighbour of every row stepped from, as if every walker swept its row itself "
+                                     "(walkers that share a sweep read the row once, so the bytes moved are fewer)"}
         if args.app == "node2vec":
             built = algorithmic_bytes(args.app, dev["scanned"], dev["steps"], total_queries, g.xadj_bits,
                                       as_built=True) / launches
@@ -560,9 +568,8 @@ def main():
                          ", scaled by algorithmic bytes",
                          "dram_frac": traffic / (per_launch_ms * 1e-3) / 1e9 / peak,
                          "issue_active": prof["issue_active"], "l2_hit_rate": prof["l2_hit_rate"],
-                         "limited_by": "instruction issue (hub rows are served by L2: DRAM traffic is below the "
-                                       "algorithmic bytes, so frac may exceed 1)"
-                         if prof["issue_active"] > 0.7 else "latency"})
+                         "limited_by": "instruction issue and latency, not HBM: shared sweeps and L2-resident hub rows keep "
+                                       "DRAM traffic far below the algorithmic bytes, so frac exceeds 1"})
         else:
             roof.update({"traffic": None, "traffic_source": "no ncu capture of this workload on kernel revision " + rev
                          if not prof else "the ncu capture of this workload is of kernel revision %s, not %s"

@@ -218,8 +218,9 @@ class Engine:
         _check(lib().fw_engine_set_sharing(self._h, mode))
 
     def set_hub_batching(self, mode):
-        """-1: when the graph has hub vertices (default), 0: never, 1: as -1 but batching to the last
-        walker.  Walkers that meet at a hub share one sweep of its row."""
+        """-1: when the graph has hub vertices and the call is large enough (default), 0: never,
+        1: whenever the graph has hubs, 2: as 1 and batching to the last walker.  Walkers that meet
+        at a hub share one sweep of its row."""
         _check(lib().fw_engine_set_hub_batching(self._h, mode))
 
     def hubs(self, which=0):

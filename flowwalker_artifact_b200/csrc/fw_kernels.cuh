@@ -20,7 +20,7 @@
 namespace fwk {
 
 // Bumped with every change of the device code that can move its counters.
-#define FW_KERNEL_REVISION "stream4k-slots"
+#define FW_KERNEL_REVISION "hub-batched-1"
 
 constexpr int kMaxSchema = 64;
 constexpr int kWarpsPerCta = 8;

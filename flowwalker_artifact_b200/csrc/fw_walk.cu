@@ -42,11 +42,16 @@ static constexpr int64_t kSharingAutoDegree = 262144;
 // (measured: R-MAT scale 22, all-vertex queries, 168 per hub: 57 ms against 61 with the higher limit;
 // scale 24, 10^7 PPR queries, about 50 per hub: 31 ms against 24).
 static constexpr int64_t kHubDenseQueries = 100;
+// A call is hub-batched at all when it brings at least this many queries per hub of the higher
+// limit: every round of the series has a fixed cost (its launches, the longest single sweep, one
+// read-back), which a short call does not earn back (R-MAT scale 22: 524,288 queries, 57 per hub,
+// take 15 ms either way; 10^6, 110 per hub, 23.4 ms batched against 24.0).
+static constexpr int64_t kHubMinQueries = 128;
 static constexpr int64_t kHubMax = (int64_t)1 << 22;
-static constexpr int64_t kHubPartSupers = 48;  // supergroups (98,304 neighbours) of a hub's row per sweeping warp, about
+static constexpr int64_t kHubPartSupers = 24;  // supergroups (49,152 neighbours) of a hub's row per sweeping warp, about
 static constexpr int64_t kHubMaxParts = 64;
 static constexpr int64_t kHubTailMin = 2048;   // parked walkers below which a call goes to its tail launch ...
-static constexpr int64_t kHubTailShare = 64;   // ... or below this share of the call's queries
+static constexpr int64_t kHubTailShare = 16;   // ... or below this share of the call's queries
 
 // Device control words of one round of a hub-batched call.
 struct HubCtl {
@@ -82,7 +87,7 @@ struct fw_engine {
   cudaStream_t stream = nullptr, stream2 = nullptr;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   // hub batching: the hub vertices and the buffers of a hub-batched call (grown on demand)
-  int hub_mode = -1;           // -1: when the graph has hubs, 0: never, 1: as -1 without the tail launch
+  int hub_mode = -1;           // -1: when it pays, 0: never, 1: whenever the graph has hubs, 2: as 1 without the tail launch
   struct HubSet {                  // the hub vertices for one limit
     int32_t n = 0;
     uint32_t limit = 0;            // a vertex is a hub iff its row has at least this many edges
@@ -266,7 +271,9 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
   if (rc) return rc;
   // Below this many parked walkers the batches are mostly empty and a round costs more than it
   // serves: the walkers left are then walked to the end by one launch, each sweeping for itself.
-  const uint32_t tail_limit = e->hub_mode == 1 ? 0u : (uint32_t)std::max<int64_t>(kHubTailMin, n / kHubTailShare);
+  const char* ts_env = getenv("FW_HUB_TAIL_SHARE");  // development aid
+  const int64_t tail_share = ts_env && atoll(ts_env) > 0 ? atoll(ts_env) : kHubTailShare;
+  const uint32_t tail_limit = e->hub_mode == 2 ? 0u : (uint32_t)std::max<int64_t>(kHubTailMin, n / tail_share);
   HubCtl* ctl = reinterpret_cast<HubCtl*>(e->d_ctl);
   FW_CUDA(cudaMemsetAsync(e->d_ctl, 0, 2 * sizeof(HubCtl), st));
   FW_CUDA(cudaMemsetAsync(hs.d_cnt, 0, keys * 8, st));
@@ -378,7 +385,8 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   // The lower hub limit when the call brings enough queries per hub to fill the batches.
   fw_engine::HubSet& hs = (e->hubset[1].n > 0 && n >= kHubDenseQueries * e->hubset[1].n) ? e->hubset[1] : e->hubset[0];
   // (node2vec's strip totals depend on the walker's previous vertex: no batching)
-  const bool hubs = e->hub_mode != 0 && hs.n > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
+  const bool worth_it = e->hub_mode > 0 || n >= kHubMinQueries * (int64_t)hs.n;
+  const bool hubs = e->hub_mode != 0 && worth_it && hs.n > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
                     p->app != FW_APP_NODE2VEC && n < ((int64_t)1 << 31) &&
                     (int64_t)hs.n * (p->app == FW_APP_METAPATH ? p->schema_len : 1) < ((int64_t)1 << 30);
   if (n > 0 && hubs) {
@@ -468,6 +476,8 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
     // Hubs: every vertex of at least `limit` neighbours, for both limits (the walk kernel of a
     // hub-batched call relies on every other row fitting one stage); a graph with more than
     // kHubMax of them runs without hub batching at that limit.
+    const char* ps_env = getenv("FW_HUB_PART_SUPERS");  // development aid
+    const int64_t part_supers = ps_env && atoll(ps_env) > 0 ? atoll(ps_env) : kHubPartSupers;
     for (int which = 0; which < 2 && g->V < INT32_MAX; ++which) {
       fw_engine::HubSet& hs = e->hubset[which];
       const int64_t limit = which ? kHubLimitLow : kHubLimitHigh;
@@ -480,7 +490,7 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
       for (size_t i = 0; i < ids.size(); ++i) {
         const int64_t b = fw::row_begin(g, ids[i]), len = fw::row_begin(g, (int64_t)ids[i] + 1) - b;
         const int64_t nq = ((b & 3) + len + 3) >> 2, n_half = (nq + kHalfQuads - 1) / kHalfQuads, supers = (n_half + 1) >> 1;
-        parts[i] = (uint16_t)std::min<int64_t>(kHubMaxParts, (supers + kHubPartSupers - 1) / kHubPartSupers);
+        parts[i] = (uint16_t)std::min<int64_t>(kHubMaxParts, (supers + part_supers - 1) / part_supers);
         hs.parts_total += parts[i];
       }
       hs.n = (int32_t)ids.size();
@@ -545,7 +555,7 @@ extern "C" int fw_engine_set_sharing(fw_engine* e, int mode) {
 }
 
 extern "C" int fw_engine_set_hub_batching(fw_engine* e, int mode) {
-  if (!e || mode < -1 || mode > 1) return fw::fail(FW_ERR_ARG, "fw_engine_set_hub_batching: mode must be -1, 0 or 1");
+  if (!e || mode < -1 || mode > 2) return fw::fail(FW_ERR_ARG, "fw_engine_set_hub_batching: mode must be -1, 0, 1 or 2");
   e->hub_mode = mode;
   return FW_OK;
 }
