@@ -59,6 +59,8 @@ def parse():
     ap.add_argument("--xadj-bits", type=int, default=32, choices=[32, 64])
     ap.add_argument("--sharing", type=int, default=-1, choices=[-1, 0, 1],
                     help="warps share very long rows: -1 by the graph's largest degree, 0 never, 1 always")
+    ap.add_argument("--hub-batching", type=int, default=-1, choices=[-1, 0, 1, 2],
+                    help="walkers that meet at a hub share a sweep: -1 when the call is large enough, 0 never, 1 always")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-strong", action="store_true", help="skip the partitioned-job legs of a multi-GPU run")
@@ -375,6 +377,7 @@ def main():
     g = make_graph(fw, args, local)
     eng = fw.Engine(g, local)
     eng.set_sharing(args.sharing)
+    eng.set_hub_batching(args.hub_batching)
     V = g.V
     n = args.queries or V
     D = args.d + 1

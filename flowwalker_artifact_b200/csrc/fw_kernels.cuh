@@ -2061,59 +2061,121 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
   }
 }
 
-// Groups the parked walkers by hub (n_hubs counts the hub-and-class keys): exclusive scan of the
-// per-key counts into `base`, one batch item per 32 walkers of a key and part of the hub's row, the
-// counts and the scatter cursors back to zero.  One CTA of kPlanThreads.
-constexpr int kPlanThreads = 1024;
-__global__ void __launch_bounds__(kPlanThreads) hub_plan_kernel(uint32_t* cnt, uint32_t* base, uint32_t* fill, int4* items,
-                                                                uint32_t* items_n, const uint16_t* __restrict__ parts,
-                                                                uint32_t* part_done, int n_hubs, int classes) {
-  __shared__ uint32_t s_wc[32], s_wb[32], s_tot[2];
+// Groups the parked walkers by hub (a key is a hub and class).  Two launches over tiles of
+// kPlanTile keys: hub_plan_count adds up every tile's walkers and batch items, and the CTA that
+// finishes last turns the tile totals into offsets; hub_plan_emit then writes every key's first
+// bucket entry (`base`), one item per 32 walkers of a key and part of the hub's row, and sets the
+// counts and the scatter cursors back to zero.
+constexpr int kPlanThreads = 1024, kPlanKeys = 4, kPlanTile = kPlanThreads * kPlanKeys;
+constexpr int kPlanMaxTiles = 1 << 16;
+
+// Sums (walkers, items) of the thread's kPlanKeys keys; exclusive offsets of the thread within the
+// CTA in (xc, xb), the CTA's totals in s_tot.  All threads of the CTA call it.
+__device__ __forceinline__ void plan_tile_scan(uint32_t my_c, uint32_t my_b, uint32_t& xc, uint32_t& xb, uint32_t* s_wc,
+                                               uint32_t* s_wb, uint32_t* s_tot) {
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-  uint32_t carry_c = 0, carry_b = 0;  // walkers and items before this tile
-  for (int tile = 0; tile < n_hubs; tile += kPlanThreads) {  // one key per thread: coalesced, scanned by shuffles
-    const int h = tile + t;
-    const uint32_t n = h < n_hubs ? cnt[h] : 0u, np = h < n_hubs ? parts[h / classes] : 0u;
-    const uint32_t nb = ((n + 31u) >> 5) * np;
-    uint32_t ic = n, ib = nb;  // inclusive scans over the warp
+  uint32_t ic = my_c, ib = my_b;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, ic, off), y = __shfl_up_sync(0xFFFFFFFFu, ib, off);
+    if (lane >= off) { ic += x; ib += y; }
+  }
+  if (lane == 31) { s_wc[warp] = ic; s_wb[warp] = ib; }
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t wc = s_wc[lane], wb = s_wb[lane];
+    uint32_t c = wc, b = wb;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
-      const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, ic, off), y = __shfl_up_sync(0xFFFFFFFFu, ib, off);
-      if (lane >= off) { ic += x; ib += y; }
+      const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, c, off), y = __shfl_up_sync(0xFFFFFFFFu, b, off);
+      if (lane >= off) { c += x; b += y; }
     }
-    if (lane == 31) { s_wc[warp] = ic; s_wb[warp] = ib; }
-    __syncthreads();
-    if (warp == 0) {  // the warps' totals -> their exclusive offsets, and the tile's totals
-      const uint32_t wc = s_wc[lane], wb = s_wb[lane];
-      uint32_t xc = wc, xb = wb;
+    s_wc[lane] = c - wc;
+    s_wb[lane] = b - wb;
+    if (lane == 31) { s_tot[0] = c; s_tot[1] = b; }
+  }
+  __syncthreads();
+  xc = s_wc[warp] + ic - my_c;
+  xb = s_wb[warp] + ib - my_b;
+}
+
+__global__ void __launch_bounds__(kPlanThreads) hub_plan_count(const uint32_t* __restrict__ cnt, const uint16_t* __restrict__ parts,
+                                                               int n_keys, int classes, uint2* tile_tot, uint32_t* tiles_done,
+                                                               uint32_t* items_n) {
+  __shared__ uint32_t s_wc[32], s_wb[32], s_tot[2];
+  __shared__ bool s_last;
+  const int t = threadIdx.x, k0 = blockIdx.x * kPlanTile + t * kPlanKeys;
+  uint32_t my_c = 0, my_b = 0;
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, xc, off), y = __shfl_up_sync(0xFFFFFFFFu, xb, off);
-        if (lane >= off) { xc += x; xb += y; }
-      }
-      s_wc[lane] = xc - wc;
-      s_wb[lane] = xb - wb;
-      if (lane == 31) { s_tot[0] = xc; s_tot[1] = xb; }
+  for (int i = 0; i < kPlanKeys; ++i)
+    if (k0 + i < n_keys) {
+      const uint32_t n = cnt[k0 + i];
+      my_c += n;
+      my_b += ((n + 31u) >> 5) * parts[(k0 + i) / classes];
     }
-    __syncthreads();
-    if (h < n_hubs) {
-      const uint32_t at = carry_c + s_wc[warp] + ic - n;
-      uint32_t it = carry_b + s_wb[warp] + ib - nb;
-      base[h] = at;
-      for (uint32_t off = 0; off < n; off += 32u) {
-        const uint32_t group = it;
-        part_done[group] = 0u;
-        for (uint32_t p = 0; p < np; ++p)
-          items[it++] = make_int4(h, (int)(at + off), (int)(min(32u, n - off) | (p << 8) | (np << 16)), (int)group);
-      }
-      if (n != 0u) cnt[h] = 0u;
-      fill[h] = 0u;
-    }
+  uint32_t xc, xb;
+  plan_tile_scan(my_c, my_b, xc, xb, s_wc, s_wb, s_tot);
+  if (t == 0) {
+    tile_tot[blockIdx.x] = make_uint2(s_tot[0], s_tot[1]);
+    __threadfence();
+    s_last = atomicAdd(tiles_done, 1u) == gridDim.x - 1u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // the last CTA: tile totals -> exclusive tile offsets, in place (nobody waits for anybody)
+  __threadfence();
+  uint32_t carry_c = 0, carry_b = 0;
+  for (int base = 0; base < (int)gridDim.x; base += kPlanThreads) {
+    const int i = base + t;
+    uint2 v = make_uint2(0u, 0u);
+    if (i < (int)gridDim.x) v = __ldcg(tile_tot + i);  // written by other CTAs: read at L2
+    __syncthreads();  // s_tot of the round before has been read
+    plan_tile_scan(v.x, v.y, xc, xb, s_wc, s_wb, s_tot);
+    if (i < (int)gridDim.x) tile_tot[i] = make_uint2(carry_c + xc, carry_b + xb);
     carry_c += s_tot[0];
     carry_b += s_tot[1];
-    __syncthreads();
   }
-  if (t == 0) *items_n = carry_b;
+  if (t == 0) {
+    *items_n = carry_b;
+    *tiles_done = 0u;
+  }
+}
+
+__global__ void __launch_bounds__(kPlanThreads) hub_plan_emit(uint32_t* cnt, uint32_t* base, uint32_t* fill, int4* items,
+                                                              const uint16_t* __restrict__ parts, uint32_t* part_done, int n_keys,
+                                                              int classes, const uint2* __restrict__ tile_off) {
+  __shared__ uint32_t s_wc[32], s_wb[32], s_tot[2];
+  const int t = threadIdx.x, k0 = blockIdx.x * kPlanTile + t * kPlanKeys;
+  uint32_t n[kPlanKeys], np[kPlanKeys], my_c = 0, my_b = 0;
+#pragma unroll
+  for (int i = 0; i < kPlanKeys; ++i) {
+    n[i] = 0u;
+    np[i] = 0u;
+    if (k0 + i < n_keys) {
+      n[i] = cnt[k0 + i];
+      np[i] = parts[(k0 + i) / classes];
+      my_c += n[i];
+      my_b += ((n[i] + 31u) >> 5) * np[i];
+    }
+  }
+  uint32_t xc, xb;
+  plan_tile_scan(my_c, my_b, xc, xb, s_wc, s_wb, s_tot);
+  const uint2 off0 = tile_off[blockIdx.x];
+  uint32_t at = off0.x + xc, it = off0.y + xb;
+#pragma unroll
+  for (int i = 0; i < kPlanKeys; ++i)
+    if (k0 + i < n_keys) {
+      base[k0 + i] = at;
+      for (uint32_t off = 0; off < n[i]; off += 32u) {
+        const uint32_t group = it;
+        part_done[group] = 0u;
+        for (uint32_t p = 0; p < np[i]; ++p)
+          items[it++] = make_int4(k0 + i, (int)(at + off), (int)(min(32u, n[i] - off) | (p << 8) | (np[i] << 16)), (int)group);
+      }
+      at += n[i];
+      if (n[i] != 0u) cnt[k0 + i] = 0u;
+      fill[k0 + i] = 0u;
+    }
 }
 
 __global__ void hub_scatter_kernel(const int32_t* __restrict__ park_hub, const int32_t* __restrict__ park_qi,

@@ -60,7 +60,7 @@ struct HubCtl {
   uint32_t park_n;               // walkers parked for this round's hub kernel
   uint32_t list_n;               // walkers listed for this round's walk kernel
   uint32_t items_n;              // batches of this round's hub kernel
-  uint32_t pad;
+  uint32_t tiles_done;           // plan: tiles counted (back to zero when the last one is)
 };
 
 
@@ -109,6 +109,7 @@ struct fw_engine {
   size_t items_cap = 0;
   unsigned long long* d_best64 = nullptr;  // [hub_cap]
   uint32_t* d_part_done = nullptr;         // [items_cap]
+  uint2* d_tile_tot = nullptr;     // plan: per tile of keys, walkers and items (then their offsets)
   unsigned char* d_ctl = nullptr;  // two HubCtl blocks
   uint32_t* h_ctl = nullptr;       // pinned word the parked count travels to
   // staging for the host-buffer entry points (grown on demand)
@@ -323,8 +324,11 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
     const int nxt = cur ^ 1;
     FW_CUDA(cudaMemsetAsync(&ctl[nxt], 0, sizeof(HubCtl), st));
     FW_CUDA(cudaMemsetAsync(e->d_best64, 0xFF, (size_t)parked * 8, st));
-    hub_plan_kernel<<<1, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, hs.d_base, hs.d_fill, e->d_items,
-                                                &ctl[cur].items_n, hs.d_parts, e->d_part_done, (int)keys, classes);
+    const int tiles = (int)((keys + kPlanTile - 1) / kPlanTile);
+    hub_plan_count<<<tiles, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, hs.d_parts, (int)keys, classes, e->d_tile_tot,
+                                                   &ctl[cur].tiles_done, &ctl[cur].items_n);
+    hub_plan_emit<<<tiles, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, hs.d_base, hs.d_fill, e->d_items, hs.d_parts,
+                                                  e->d_part_done, (int)keys, classes, e->d_tile_tot);
     const int sgrid = (int)std::min<int64_t>(((int64_t)parked + 255) / 256, (int64_t)e->sms * 8);
     hub_scatter_kernel<<<sgrid, 256, 0, st>>>(e->d_park_hub[cur], e->d_park_qi[cur], &ctl[cur].park_n, hs.d_base, hs.d_fill,
                                               e->d_bucket);
@@ -340,7 +344,7 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
     a.hub.list = e->d_list; a.hub.list_n = &ctl[nxt].list_n; a.hub.work = &ctl[nxt].work_walk;
     const int wgrid = (int)std::min<int64_t>(full_walk, std::max<int64_t>(((int64_t)parked + 31) / 32, 1));
     FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(wgrid), dim3(kThreads), params, walk_smem, st));
-    *launches += 4;
+    *launches += 5;
     cur = nxt;
   }
   return FW_OK;
@@ -388,7 +392,7 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   const bool worth_it = e->hub_mode > 0 || n >= kHubMinQueries * (int64_t)hs.n;
   const bool hubs = e->hub_mode != 0 && worth_it && hs.n > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
                     p->app != FW_APP_NODE2VEC && n < ((int64_t)1 << 31) &&
-                    (int64_t)hs.n * (p->app == FW_APP_METAPATH ? p->schema_len : 1) < ((int64_t)1 << 30);
+                    (int64_t)hs.n * (p->app == FW_APP_METAPATH ? p->schema_len : 1) <= (int64_t)kPlanMaxTiles * kPlanTile / 2;
   if (n > 0 && hubs) {
     const int hrc = run_hub_batched(e, hs, p, a, n, st, smem, launches);
     if (hrc) return hrc;
@@ -501,6 +505,7 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
       FW_CUDA(cudaMemcpy(hs.d_parts, parts.data(), parts.size() * 2, cudaMemcpyHostToDevice));
     }
     if (e->hubset[0].n > 0 || e->hubset[1].n > 0) {
+      FW_CUDA(cudaMalloc(&e->d_tile_tot, (size_t)kPlanMaxTiles * sizeof(uint2)));
       FW_CUDA(cudaMalloc(&e->d_ctl, 2 * sizeof(HubCtl)));
       FW_CUDA(cudaMallocHost(&e->h_ctl, 64));
     }
@@ -536,7 +541,7 @@ extern "C" void fw_engine_destroy(fw_engine* e) {
   cudaFree(e->d_scratch);
   if (e->h_scratch) cudaFreeHost(e->h_scratch);
   for (auto& hs : e->hubset) { cudaFree(hs.d_ids); cudaFree(hs.d_cnt); cudaFree(hs.d_base); cudaFree(hs.d_fill); cudaFree(hs.d_parts); }
-  cudaFree(e->d_ctl);
+  cudaFree(e->d_ctl); cudaFree(e->d_tile_tot);
   if (e->h_ctl) cudaFreeHost(e->h_ctl);
   cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
   cudaFree(e->d_best64); cudaFree(e->d_part_done);
