@@ -1439,7 +1439,8 @@ __host__ __device__ constexpr bool hub_parks(int hubs) { return hubs == kHubPark
 __host__ __device__ constexpr uint32_t hub_staged_quads(int hubs) { return staged_quads(hubs == kHubParkLow ? kHubLimitLow : kHubLimitHigh); }
 template <int APP, int MODE, bool CLEAN, typename OffT, int HUBS>
 constexpr int walk_min_blocks() {
-  return HUBS == kHubParkLow ? 4 : HUBS == kHubPark ? 3 : min_blocks<APP, MODE, CLEAN, OffT>();
+  return APP == FW_APP_NODE2VEC ? min_blocks<APP, MODE, CLEAN, OffT>()
+       : HUBS == kHubParkLow ? 4 : HUBS == kHubPark ? 3 : min_blocks<APP, MODE, CLEAN, OffT>();
 }
 template <int APP, int MODE, bool CLEAN, typename OffT, int HUBS = kHubOff>
 __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, OffT, HUBS>()) walk_kernel(const __grid_constant__ WalkArgs a) {
@@ -1448,7 +1449,8 @@ __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, Of
   __shared__ uint32_t s_flags[APP == FW_APP_NODE2VEC ? kWarpsPerCta : 1][32];  // node2vec match flags
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   constexpr uint32_t kStagedQuads = hub_staged_quads(HUBS);
-  constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_EDGE ? 0u : hub_parks(HUBS) ? 2u * 16u * kStagedQuads : ring_bytes<APP>();
+  constexpr uint32_t kRingPerWarp = MODE == FW_GROUP_EDGE ? 0u
+                                  : (hub_parks(HUBS) && APP != FW_APP_NODE2VEC) ? 2u * 16u * kStagedQuads : ring_bytes<APP>();
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
   const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
   Ring ring;
@@ -1501,31 +1503,52 @@ __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, Of
   unsigned long long* const work = HUBS != kHubOff ? a.hub.work : a.scratch + kSlotCounter;
   const long long n_work = (HUBS != kHubOff && a.hub.list != nullptr) ? (long long)*a.hub.list_n : (long long)a.n;
   FW_PROF(unsigned long long prof_t[3] = {0, 0, 0}, prof_n[3] = {0, 0, 0}, prof_sub = 0; const long long prof_begin = clock64();)
-  if constexpr (kSlots == 1 && HUBS == kHubOff) {
-    // One query per warp, walked to its end with all state in uniform registers (node2vec: its
-    // kernels are the largest, and the slot bookkeeping below cost them a third of their speed).
+  if constexpr (kSlots == 1) {
+    // One query per warp, walked to its end (or, in a hub-batched series, to the next hub) with all
+    // state in uniform registers (node2vec: its kernels are the largest, and the slot bookkeeping
+    // below cost them a third of their speed).
+    const bool resumed = HUBS != kHubOff && a.hub.list != nullptr;
     while (!ring.failed) {
       long long first = 0;
       if (lane == 0) first = (long long)atomicAdd(work, (unsigned long long)kMinClaim);
       first = __shfl_sync(0xFFFFFFFFu, first, 0);
       if (first >= n_work) break;
       const long long stop = first + kMinClaim < n_work ? first + kMinClaim : n_work;
-      for (long long q1 = first; q1 < stop && !ring.failed; ++q1) {
+      for (long long idx = first; idx < stop && !ring.failed; ++idx) {
+        const long long q1 = resumed ? (long long)__ldg(a.hub.list + idx) : idx;
         const uint64_t qid = a.qid_base + (uint64_t)q1 * a.qid_stride;
         const uint32_t ql = (uint32_t)qid, qh = (uint32_t)(qid >> 32);
         int32_t* __restrict__ row_out = a.result + q1 * D;
-        int32_t at = __ldg(a.starts + q1);
-        if (lane == 0) row_out[0] = at;
         StepCtx c;
         c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u;
         c.flags = &s_flags[APP == FW_APP_NODE2VEC ? warp : 0][0];
         int kk = 0;
+        int32_t at;
+        if (resumed) {  // a walker a hub launch moved on: position and previous vertex from the table
+          kk = a.hub.kstate[q1];
+          at = row_out[kk];
+          if (kk > 0) {
+            c.prev = row_out[kk - 1];
+            const int64_t pb0 = (int64_t)__ldg(xadj + c.prev);
+            c.prow = a.adj + pb0;
+            c.plen = (uint32_t)((int64_t)__ldg(xadj + c.prev + 1) - pb0);
+          }
+        } else {
+          at = __ldg(a.starts + q1);
+          if (lane == 0) row_out[0] = at;
+        }
+        bool parked = false;
         if (at < 0 || (int64_t)at >= a.V) {
           status |= FW_STATUS_BAD_START;
         } else {
           while (kk < a.d) {
             const int64_t b = (int64_t)__ldg(xadj + at), e = (int64_t)__ldg(xadj + at + 1);
             if (e <= b) break;
+            if (hub_parks(HUBS) && (uint64_t)(e - b) >= (uint64_t)a.hub.min_degree) {
+              if (lane == 0) hub_park(a.hub, q1, kk, at);  // the hub launch takes the walker from here
+              parked = true;
+              break;
+            }
             const int64_t q0 = b >> 2;
             c.prim = prim_base + q0;
             c.sec = sec_base + q0;
@@ -1549,6 +1572,7 @@ __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, Of
             }
           }
         }
+        if (parked) continue;
         for (int z = kk + 1 + (int)lane; z <= a.d; z += 32) row_out[z] = -1;
         my_steps += (unsigned long long)kk;
         if (lane == 0) {
@@ -2061,6 +2085,222 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
   }
 }
 
+// The hub kernel of node2vec.  The sweep of a row reads plain weights, which do not depend on the
+// walker; what does -- the bias factors 1/p, 1, 1/q by the walker's previous vertex -- enters per
+// strip, and only for the strips whose optimistic key can still win (n2v_test).  So the row is swept
+// once per batch, and after every third supergroup the warp goes through the batch walker by walker:
+// the lanes stand for the strips, as in a walker's own sweep, and form that walker's Philox words;
+// n2v_test evaluates the few strips it has to.  A walker's best (key, strip, pick word, total) lives
+// in the registers of the lane with the walker's number between its turns.  Rows are not split.
+template <bool CLEAN, typename OffT>
+__global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel_n2v(const __grid_constant__ WalkArgs a) {
+  constexpr int SAPP = kAppPlainCompact;  // plain weights
+  extern __shared__ __align__(128) unsigned char s_dyn[];
+  __shared__ __align__(8) unsigned long long s_bar[kWarpsPerCta][2];
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  constexpr uint32_t kRingPerWarp = ring_bytes<FW_APP_DEEPWALK>();
+  uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_dyn + kRingPerWarp * kWarpsPerCta);
+  const unsigned char* ring_ptr = s_dyn + kRingPerWarp * warp;
+  Ring ring;
+  ring.data = smem_addr(ring_ptr);
+  ring.bar = smem_addr(&s_bar[warp][0]);
+  ring.parity = 0u;
+  ring.failed = false;
+  if (lane == 0) {
+    mbar_init(ring.bar, 1u);
+    mbar_init(ring.bar + 8u, 1u);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (a.hist_in_smem)
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x) s_hist[z] = 0u;
+  __syncthreads();
+
+  const OffT* __restrict__ xadj = static_cast<const OffT*>(a.xadj);
+  const int64_t D = (int64_t)a.d + 1;
+  const int4* const prim_base = reinterpret_cast<const int4*>(a.weight);
+  const int4* const sec_base = reinterpret_cast<const int4*>(a.adj);
+  const int4* const lane_ptr = reinterpret_cast<const int4*>(ring_ptr) + lane;
+  const uint32_t n_items = *a.hub.items_n;
+  unsigned long long my_steps = 0, my_scanned = 0;
+  uint32_t status = 0;
+
+  while (!ring.failed) {
+    unsigned long long item = 0;
+    if (lane == 0) item = atomicAdd(a.hub.work, 1ull);
+    item = __shfl_sync(0xFFFFFFFFu, item, 0);
+    if (item >= (unsigned long long)n_items) break;
+    const int4 it = __ldg(a.hub.items + item);
+    const uint32_t n_in = (uint32_t)it.z & 0xFFu;
+    const int32_t v = __ldg(a.hub.hub_ids + it.x);
+    const int64_t b = (int64_t)__ldg(xadj + v);
+    const uint32_t len = (uint32_t)((int64_t)__ldg(xadj + v + 1) - b);
+    const int64_t q0 = b >> 2;
+    StepCtx c;
+    c.prim = prim_base + q0;
+    c.sec = sec_base + q0;
+    c.head = (uint32_t)(b - 4 * q0);
+    c.tail = c.head + len;
+    c.nq = (c.tail + 3u) >> 2;
+    c.prev = -1; c.prow = a.adj; c.plen = 0u; c.want = 0; c.from = 0u; c.flags = nullptr;
+    // the walker of this lane: query, steps so far, previous vertex and its row
+    const bool have = lane < n_in;
+    const long long qi = have ? (long long)__ldg(a.hub.bucket + it.y + lane) : 0;
+    int32_t k = have ? a.hub.kstate[qi] : 0;
+    const uint64_t qid = a.qid_base + (uint64_t)qi * a.qid_stride;
+    const uint32_t qlo = (uint32_t)qid, qhi = (uint32_t)(qid >> 32);
+    int32_t wprev = -1;
+    long long wpb = 0;
+    uint32_t wplen = 0;
+    if (have && k > 0) {
+      wprev = a.result[qi * D + k - 1];
+      wpb = (long long)__ldg(xadj + wprev);
+      wplen = (uint32_t)((long long)__ldg(xadj + wprev + 1) - wpb);
+    }
+    uint32_t bkey = 0xFFFFFFFFu, bid = 0xFFFFFFFFu, bpick = 0u;
+    float bW = 0.0f;
+
+    const uint32_t n_half = (c.nq + kHalfQuads - 1u) / kHalfQuads;
+    const uint32_t end_super = ((n_half + 1u) >> 1) - 1u;
+    if (lane == 0) {
+      half_fill(c, ring, 0u);
+      if (n_half > 1u) half_fill(c, ring, 1u);
+    }
+    float W0 = 0.0f, W1 = 0.0f, W2 = 0.0f;
+    uint32_t g = 0, m = 0;
+#pragma unroll 1
+    for (uint32_t sg = 0;; ++sg) {
+      const bool last = sg == end_super;
+      float W;
+      bool ok;
+      if (sg == 0u || last) ok = super_turn<SAPP, CLEAN, true>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
+      else ok = super_turn<SAPP, CLEAN, false>(c, sg, n_half, n_half, lane, ring, lane_ptr, W);
+      if (!ok) { ring.failed = true; break; }
+      if (m == 0u) W0 = W; else if (m == 1u) W1 = W; else W2 = W;
+      if (m == 2u || last) {
+        // the batch, walker by walker: lanes are strips
+#pragma unroll 1
+        for (uint32_t q = 0; q < n_in; ++q) {
+          c.prev = __shfl_sync(0xFFFFFFFFu, wprev, (int)q);
+          c.prow = a.adj + __shfl_sync(0xFFFFFFFFu, wpb, (int)q);
+          c.plen = __shfl_sync(0xFFFFFFFFu, wplen, (int)q);
+          const uint32_t c1 = (uint32_t)__shfl_sync(0xFFFFFFFFu, k, (int)q) | (fw::kPurposeScan << 28);
+          const uint32_t ql = __shfl_sync(0xFFFFFFFFu, qlo, (int)q), qh = __shfl_sync(0xFFFFFFFFu, qhi, (int)q);
+          Best best{__shfl_sync(0xFFFFFFFFu, bkey, (int)q), __shfl_sync(0xFFFFFFFFu, bid, (int)q),
+                    __shfl_sync(0xFFFFFFFFu, bpick, (int)q), __shfl_sync(0xFFFFFFFFu, bW, (int)q)};
+          const fw::Philox4 r = fw::philox4x32_10(g * 32u + lane, c1, ql, qh, a.k0, a.k1);
+#pragma unroll 1
+          for (uint32_t i = 0; i <= m; ++i) {
+            const float Wi = i == 0u ? W0 : i == 1u ? W1 : W2;
+            const uint32_t x = i == 0u ? r.x : i == 1u ? r.y : r.z;
+            const uint32_t s = 3u * g + i;
+            if (c.prev >= 0) {
+              n2v_test<CLEAN>(a, c, s, lane, Wi, x, r.w, best);
+            } else {
+              // first step of a query that starts at the hub: plain weights, every strip's key
+              uint32_t key = 0xFFFFFFFFu, id = 0xFFFFFFFFu;
+              if (Wi > 0.0f) { key = __float_as_uint(__fdiv_rn(fw::exp_key(x), Wi)); id = s * 32u + lane; }
+              warp_argmin(key, id);
+              if (id != 0xFFFFFFFFu && (key < best.key || (key == best.key && id < best.id))) {
+                best.key = key; best.id = id;
+                best.pick = __shfl_sync(0xFFFFFFFFu, r.w, (int)(id & 31u));
+                best.W = __shfl_sync(0xFFFFFFFFu, Wi, (int)(id & 31u));
+              }
+            }
+          }
+          if (lane == q) { bkey = best.key; bid = best.id; bpick = best.pick; bW = best.W; }
+        }
+        W0 = 0.0f; W1 = 0.0f; W2 = 0.0f;
+        m = 0u;
+        ++g;
+      } else {
+        ++m;
+      }
+      if (last) break;
+    }
+    if (ring.failed) break;
+
+    // ---- the pick inside every walker's winning strip, walker by walker ----
+    uint32_t rel = 0xFFFFFFFFu;
+#pragma unroll 1
+    for (uint32_t q = 0; q < n_in; ++q) {
+      const uint32_t B = __shfl_sync(0xFFFFFFFFu, bid, (int)q);
+      if (B == 0xFFFFFFFFu) continue;  // warp-uniform
+      c.prev = __shfl_sync(0xFFFFFFFFu, wprev, (int)q);
+      c.prow = a.adj + __shfl_sync(0xFFFFFFFFu, wpb, (int)q);
+      c.plen = __shfl_sync(0xFFFFFFFFu, wplen, (int)q);
+      const uint32_t pick = __shfl_sync(0xFFFFFFFFu, bpick, (int)q);
+      const float WB = __shfl_sync(0xFFFFFFFFu, bW, (int)q);
+      const uint32_t r1 = c.prev >= 0 ? n2v_pick<CLEAN>(a, c, B, pick, lane) : pick_in_row<SAPP, CLEAN>(a, c, B, pick, WB, lane);
+      if (lane == q) rel = r1;
+    }
+
+    // ---- every walker takes its step ----
+    bool fin = false;
+    if (have) {
+      if (rel == 0xFFFFFFFFu) {
+        fin = true;  // no edge with a positive bias
+      } else {
+        const int32_t nxt = __ldg(a.adj + (4 * q0 + (int64_t)rel));
+        if (nxt < 0 || (int64_t)nxt >= a.V) {
+          status |= FW_STATUS_BAD_NEIGHBOR;
+          fin = true;
+        } else {
+          a.result[qi * D + k + 1] = nxt;
+          my_scanned += (unsigned long long)len;
+          ++k;
+          if (k >= a.d) {
+            fin = true;
+          } else {
+            const OffT nb = __ldg(xadj + nxt), ne = __ldg(xadj + nxt + 1);
+            if (ne <= nb) {
+              fin = true;  // dead end
+            } else if ((uint64_t)(ne - nb) >= (uint64_t)a.hub.min_degree) {
+              hub_park(a.hub, qi, k, nxt);
+            } else {
+              const uint32_t pos = atomicAdd(a.hub.next_n, 1u);
+              a.hub.next_list[pos] = (int32_t)qi;
+              a.hub.kstate[qi] = k;
+            }
+          }
+        }
+      }
+    }
+    for (uint32_t mm = __ballot_sync(0xFFFFFFFFu, fin); mm != 0u; mm &= mm - 1u) {
+      const int s = __ffs((int)mm) - 1;
+      const long long qs = __shfl_sync(0xFFFFFFFFu, qi, s);
+      const int ks = __shfl_sync(0xFFFFFFFFu, k, s);
+      int32_t* __restrict__ row_out = a.result + qs * D;
+      for (int z = ks + 1 + (int)lane; z <= a.d; z += 32) row_out[z] = -1;
+    }
+    if (fin) {
+      my_steps += (unsigned long long)k;
+      if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
+      else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+    }
+  }
+  if (ring.failed) {
+    status |= FW_STATUS_WAIT_TIMEOUT;
+    mbar_wait(ring.bar, ring.parity & 1u);
+    mbar_wait(ring.bar + 8u, (ring.parity >> 1) & 1u);
+  }
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    my_steps += __shfl_xor_sync(0xFFFFFFFFu, my_steps, off);
+    my_scanned += __shfl_xor_sync(0xFFFFFFFFu, my_scanned, off);
+  }
+  status = __reduce_or_sync(0xFFFFFFFFu, status);
+  if (lane == 0) {
+    if (my_steps) atomicAdd(a.scratch + kSlotSteps, my_steps);
+    if (my_scanned) atomicAdd(a.scratch + kSlotScanned, my_scanned);
+    if (status) atomicOr(a.scratch + kSlotStatus, (unsigned long long)status);
+  }
+  if (a.hist_in_smem) {
+    __syncthreads();
+    for (int z = threadIdx.x; z <= a.d; z += blockDim.x)
+      if (s_hist[z]) atomicAdd(a.scratch + kSlotHist + z, (unsigned long long)s_hist[z]);
+  }
+}
+
 // Groups the parked walkers by hub (a key is a hub and class).  Two launches over tiles of
 // kPlanTile keys: hub_plan_count adds up every tile's walkers and batch items, and the CTA that
 // finishes last turns the tile totals into offsets; hub_plan_emit then writes every key's first
@@ -2210,7 +2450,15 @@ inline KernelFn pick_hub_kernel_of(int which, bool clean, int xadj_bits) {
        : which == 2 ? pick_hub_walk<APP, kHubTail>(clean, xadj_bits)
        : which == 3 ? pick_hub_walk<APP, kHubParkLow>(clean, xadj_bits) : pick_hub_walk<APP, kHubPark>(clean, xadj_bits);
 }
+inline KernelFn pick_hub_kernel_n2v(int which, bool clean, int xadj_bits) {
+  if (which == 1) {
+    if (xadj_bits == 64) return clean ? (KernelFn)hub_kernel_n2v<true, int64_t> : (KernelFn)hub_kernel_n2v<false, int64_t>;
+    return clean ? (KernelFn)hub_kernel_n2v<true, uint32_t> : (KernelFn)hub_kernel_n2v<false, uint32_t>;
+  }
+  return which == 2 ? pick_hub_walk<FW_APP_NODE2VEC, kHubTail>(clean, xadj_bits) : pick_hub_walk<FW_APP_NODE2VEC, kHubPark>(clean, xadj_bits);
+}
 inline KernelFn pick_hub_kernel(int app, int which, bool clean, int xadj_bits) {
+  if (app == FW_APP_NODE2VEC) return pick_hub_kernel_n2v(which, clean, xadj_bits);
   if (app == FW_APP_PPR) return pick_hub_kernel_of<FW_APP_PPR>(which, clean, xadj_bits);
   if (app == FW_APP_METAPATH) return pick_hub_kernel_of<FW_APP_METAPATH>(which, true, xadj_bits);  // 0/1 biases: nothing to clamp
   return pick_hub_kernel_of<FW_APP_DEEPWALK>(which, clean, xadj_bits);

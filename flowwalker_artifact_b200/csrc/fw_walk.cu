@@ -97,6 +97,7 @@ struct fw_engine {
     uint32_t* d_fill = nullptr;    // [n * classes]
     int classes_cap = 0;           // classes the three arrays above are sized for
     uint16_t* d_parts = nullptr;   // [n] parts the sweep of a hub's row is split into
+    uint16_t* d_ones = nullptr;    // [n] the same for node2vec, whose hub kernel does not split rows
     uint64_t parts_total = 0;      // their sum
   } hubset[2];                     // 0: limit 1,016, 1: limit 504
   size_t hub_cap = 0;              // queries the buffers below are sized for
@@ -265,9 +266,13 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
   KernelFn hub_fn = pick_hub_kernel(p->app, 1, e->clean_weights, e->xadj_bits);
   KernelFn tail_fn = pick_hub_kernel(p->app, 2, e->clean_weights, e->xadj_bits);
   int walk_per_sm = 0, hub_per_sm = 0, tail_per_sm = 0;
-  const size_t walk_smem = hub_walk_smem_bytes(hs.limit, p->d, a.hist_in_smem != 0);
+  // node2vec's walk kernels keep their own ring; its hub kernel sweeps like the others'
+  const bool n2v = p->app == FW_APP_NODE2VEC;
+  const size_t walk_smem = n2v ? smem : hub_walk_smem_bytes(hs.limit, p->d, a.hist_in_smem != 0);
+  const size_t hub_smem = kernel_smem_bytes(FW_APP_DEEPWALK, FW_GROUP_STRIP, p->d, a.hist_in_smem != 0);
+  const uint16_t* d_parts = n2v ? hs.d_ones : hs.d_parts;
   rc = prepare_kernel(walk_fn, walk_smem, &walk_per_sm);
-  if (!rc) rc = prepare_kernel(hub_fn, smem, &hub_per_sm);
+  if (!rc) rc = prepare_kernel(hub_fn, hub_smem, &hub_per_sm);
   if (!rc) rc = prepare_kernel(tail_fn, smem, &tail_per_sm);
   if (rc) return rc;
   // Below this many parked walkers the batches are mostly empty and a round costs more than it
@@ -281,7 +286,7 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
   a.hub.hub_ids = hs.d_ids; a.hub.n_hubs = hs.n; a.hub.min_degree = hs.limit; a.hub.classes = classes;
   a.hub.kstate = e->d_kstate;
   a.hub.next_list = e->d_list; a.hub.bucket = e->d_bucket; a.hub.items = e->d_items;
-  a.hub.hub_parts = hs.d_parts; a.hub.best64 = e->d_best64; a.hub.part_done = e->d_part_done;
+  a.hub.hub_parts = d_parts; a.hub.best64 = e->d_best64; a.hub.part_done = e->d_part_done;
   auto parks_into = [&](int set) {
     a.hub.park_hub = e->d_park_hub[set]; a.hub.park_qi = e->d_park_qi[set];
     a.hub.park_n = &ctl[set].park_n; a.hub.hub_cnt = hs.d_cnt + (size_t)set * keys;
@@ -325,9 +330,9 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
     FW_CUDA(cudaMemsetAsync(&ctl[nxt], 0, sizeof(HubCtl), st));
     FW_CUDA(cudaMemsetAsync(e->d_best64, 0xFF, (size_t)parked * 8, st));
     const int tiles = (int)((keys + kPlanTile - 1) / kPlanTile);
-    hub_plan_count<<<tiles, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, hs.d_parts, (int)keys, classes, e->d_tile_tot,
+    hub_plan_count<<<tiles, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, d_parts, (int)keys, classes, e->d_tile_tot,
                                                    &ctl[cur].tiles_done, &ctl[cur].items_n);
-    hub_plan_emit<<<tiles, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, hs.d_base, hs.d_fill, e->d_items, hs.d_parts,
+    hub_plan_emit<<<tiles, kPlanThreads, 0, st>>>(hs.d_cnt + (size_t)cur * keys, hs.d_base, hs.d_fill, e->d_items, d_parts,
                                                   e->d_part_done, (int)keys, classes, e->d_tile_tot);
     const int sgrid = (int)std::min<int64_t>(((int64_t)parked + 255) / 256, (int64_t)e->sms * 8);
     hub_scatter_kernel<<<sgrid, 256, 0, st>>>(e->d_park_hub[cur], e->d_park_qi[cur], &ctl[cur].park_n, hs.d_base, hs.d_fill,
@@ -339,7 +344,7 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
     a.hub.list = nullptr; a.hub.list_n = nullptr;
     const int64_t max_items = ((int64_t)parked / 32) * kHubMaxParts + (int64_t)hs.parts_total * classes;
     const int hgrid = (int)std::min<int64_t>(full_hub, std::max<int64_t>((max_items + 7) / 8, 1));
-    FW_CUDA(cudaLaunchKernel((const void*)hub_fn, dim3(hgrid), dim3(kThreads), params, smem, st));
+    FW_CUDA(cudaLaunchKernel((const void*)hub_fn, dim3(hgrid), dim3(kThreads), params, hub_smem, st));
     // walk kernel: the walkers the hub kernel listed
     a.hub.list = e->d_list; a.hub.list_n = &ctl[nxt].list_n; a.hub.work = &ctl[nxt].work_walk;
     const int wgrid = (int)std::min<int64_t>(full_walk, std::max<int64_t>(((int64_t)parked + 31) / 32, 1));
@@ -383,15 +388,16 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   const size_t words = (size_t)kSlotHist + (size_t)p->d + 1;
   FW_CUDA(cudaMemsetAsync(d_scratch, 0, words * 8, st));
   FW_CUDA(cudaEventRecord(ev_begin, st));
-  // Hub batching: DeepWalk, PPR and MetaPath (the strip totals of a row do not depend on the walker,
-  // for MetaPath on the label it wants) with the strip sampler, on graphs that have hub vertices.
-  // Query and vertex numbers must fit 31 bits.
+  // Hub batching, with the strip sampler on graphs that have hub vertices: the strip totals of a row
+  // do not depend on the walker (MetaPath: on the label it wants; node2vec: the plain totals its
+  // sweep forms).  Query and vertex numbers must fit 31 bits.
   // The lower hub limit when the call brings enough queries per hub to fill the batches.
-  fw_engine::HubSet& hs = (e->hubset[1].n > 0 && n >= kHubDenseQueries * e->hubset[1].n) ? e->hubset[1] : e->hubset[0];
-  // (node2vec's strip totals depend on the walker's previous vertex: no batching)
+  // (node2vec: the higher limit always; its walk kernel stages nothing)
+  fw_engine::HubSet& hs = (p->app != FW_APP_NODE2VEC && e->hubset[1].n > 0 && n >= kHubDenseQueries * e->hubset[1].n)
+                              ? e->hubset[1] : e->hubset[0];
   const bool worth_it = e->hub_mode > 0 || n >= kHubMinQueries * (int64_t)hs.n;
   const bool hubs = e->hub_mode != 0 && worth_it && hs.n > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
-                    p->app != FW_APP_NODE2VEC && n < ((int64_t)1 << 31) &&
+                    n < ((int64_t)1 << 31) &&
                     (int64_t)hs.n * (p->app == FW_APP_METAPATH ? p->schema_len : 1) <= (int64_t)kPlanMaxTiles * kPlanTile / 2;
   if (n > 0 && hubs) {
     const int hrc = run_hub_batched(e, hs, p, a, n, st, smem, launches);
@@ -503,6 +509,9 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
       FW_CUDA(cudaMemcpy(hs.d_ids, ids.data(), ids.size() * 4, cudaMemcpyHostToDevice));
       FW_CUDA(cudaMalloc(&hs.d_parts, parts.size() * 2));
       FW_CUDA(cudaMemcpy(hs.d_parts, parts.data(), parts.size() * 2, cudaMemcpyHostToDevice));
+      std::fill(parts.begin(), parts.end(), (uint16_t)1);
+      FW_CUDA(cudaMalloc(&hs.d_ones, parts.size() * 2));
+      FW_CUDA(cudaMemcpy(hs.d_ones, parts.data(), parts.size() * 2, cudaMemcpyHostToDevice));
     }
     if (e->hubset[0].n > 0 || e->hubset[1].n > 0) {
       FW_CUDA(cudaMalloc(&e->d_tile_tot, (size_t)kPlanMaxTiles * sizeof(uint2)));
@@ -540,7 +549,7 @@ extern "C" void fw_engine_destroy(fw_engine* e) {
   cudaFree(e->d_xadj); cudaFree(e->d_adj); cudaFree(e->d_weight); cudaFree(e->d_label);
   cudaFree(e->d_scratch);
   if (e->h_scratch) cudaFreeHost(e->h_scratch);
-  for (auto& hs : e->hubset) { cudaFree(hs.d_ids); cudaFree(hs.d_cnt); cudaFree(hs.d_base); cudaFree(hs.d_fill); cudaFree(hs.d_parts); }
+  for (auto& hs : e->hubset) { cudaFree(hs.d_ids); cudaFree(hs.d_cnt); cudaFree(hs.d_base); cudaFree(hs.d_fill); cudaFree(hs.d_parts); cudaFree(hs.d_ones); }
   cudaFree(e->d_ctl); cudaFree(e->d_tile_tot);
   if (e->h_ctl) cudaFreeHost(e->h_ctl);
   cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);

@@ -98,7 +98,8 @@ def test_star_hub_shared_between_warps(app, kw, n):
 
 
 @pytest.mark.parametrize("hub", [0, 1, 2])
-@pytest.mark.parametrize("app,kw", APPS[:2] + [APPS[3], (fw.APP_METAPATH, dict(d=7, schema=[3, 3, 0]))])
+@pytest.mark.parametrize("app,kw", APPS + [(fw.APP_METAPATH, dict(d=7, schema=[3, 3, 0])),
+                                          (fw.APP_NODE2VEC, dict(d=80, p=0.25, q=4.0))])
 def test_hub_batching_on_and_off(app, kw, hub):
     """Walkers that meet at a vertex of 1,024 or more neighbours share one sweep of its row (a walk
     call is then a series of launches); with it switched off every walker sweeps for itself in one
