@@ -65,6 +65,10 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-strong", action="store_true", help="skip the partitioned-job legs of a multi-GPU run")
     ap.add_argument("--no-numa", action="store_true", help="leave the rank's CPU affinity as it is")
+    ap.add_argument("--early-delivery", type=int, default=-1, choices=[-1, 0, 1, 2],
+                    help="end-to-end leg: -1 rows of ended walks go to the host table while the others walk on where "
+                         "the walk is long enough (fw_engine_set_early_delivery), 0 one copy of the table after the "
+                         "last launch, 1 always deliver, 2 deliver then fall back to the copy")
     ap.add_argument("--e2e-batches", type=int, default=1, help="double-buffered batches of the end-to-end leg")
     return ap.parse_args()
 
@@ -378,6 +382,7 @@ def main():
     eng = fw.Engine(g, local)
     eng.set_sharing(args.sharing)
     eng.set_hub_batching(args.hub_batching)
+    eng.set_early_delivery(args.early_delivery)
     V = g.V
     n = args.queries or V
     D = args.d + 1
@@ -592,7 +597,12 @@ def main():
             line["e2e"] = {"value": e2e["steps"] / (e2e["ms"] * 1e-3), "unit": "walk steps/s",
                            "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 4 * n * D,
                            "ms_per_step": e2e["ms"] / args.steps, "clocks": e2e["clocks"],
-                           "d2h_only_gbs_per_rank": copy_gbs, "numa": numa}
+                           "d2h_only_gbs_per_rank": copy_gbs, "numa": numa,
+                           "launches": e2e["launches"], "kernel_ms_per_step": e2e["kernel_ms"] / args.steps,
+                           "early_delivery": "on: rows of ended walks are written to the page-locked host table by "
+                                             "deliver_kernel during the series (its launches are counted in `launches`)"
+                                             if args.early_delivery != 0 and e2e["launches"] > dev["launches"]
+                                             else "off: one copy of the table after the last launch"}
         if strong:
             line["strong"] = strong
         if world == 1 and not args.no_cpu_baseline:

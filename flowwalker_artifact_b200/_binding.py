@@ -78,6 +78,7 @@ def lib():
         L.fw_engine_device.argtypes = [vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         L.fw_engine_set_sharing.argtypes = [vp, ctypes.c_int]
         L.fw_engine_set_hub_batching.argtypes = [vp, ctypes.c_int]
+        L.fw_engine_set_early_delivery.argtypes = [vp, ctypes.c_int]
         L.fw_engine_hubs.argtypes = [vp, ctypes.c_int, ctypes.POINTER(i32), ctypes.POINTER(ctypes.c_uint32)]
         L.fw_walk_device.argtypes = [vp, ctypes.POINTER(_Params), vp, i64, vp, vp,
                                      ctypes.POINTER(WalkStats), vp]
@@ -222,6 +223,13 @@ class Engine:
         1: whenever the graph has hubs, 2: as 1 and batching to the last walker.  Walkers that meet
         at a hub share one sweep of its row."""
         _check(lib().fw_engine_set_hub_batching(self._h, mode))
+
+    def set_early_delivery(self, mode):
+        """-1 (default): a hub-batched call whose result buffer is page-locked host memory writes
+        the rows of ended walks to it while the others walk on, where the walk is long enough for
+        that to pay; 0: one copy after the last launch; 1: always deliver; 2: deliver, then fall
+        back to the copy (1 and 2 are for tests)."""
+        _check(lib().fw_engine_set_early_delivery(self._h, mode))
 
     def hubs(self, which=0):
         """(number of hub vertices, row length from which a vertex is a hub) for the limit of

@@ -20,7 +20,7 @@
 namespace fwk {
 
 // Bumped with every change of the device code that can move its counters.
-#define FW_KERNEL_REVISION "hub-batched-1"
+#define FW_KERNEL_REVISION "hub-batched-2"
 
 constexpr int kMaxSchema = 64;
 constexpr int kWarpsPerCta = 8;
@@ -92,6 +92,8 @@ struct HubArgs {
   unsigned long long* best64; // split rows: smallest (key << 32 | strip id) per bucket entry over the parts done
   uint32_t* part_done;        // split rows: parts done, per group (index of the group's first item)
   unsigned long long* work; // work counter of this launch
+  int32_t* fin;             // per query: the tag of the launch its walk ended in (0: still walking), or nullptr;
+  int32_t fin_tag;          // deliver_kernel copies the rows of ended walks to the caller's host table by tag
 };
 
 struct WalkArgs {
@@ -1578,6 +1580,7 @@ __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, Of
         if (lane == 0) {
           if (a.hist_in_smem) atomicAdd(&s_hist[kk], 1u);
           else atomicAdd(a.scratch + kSlotHist + kk, 1ull);
+          if (HUBS != kHubOff && a.hub.fin) a.hub.fin[q1] = a.hub.fin_tag;
         }
       }
     }
@@ -1751,6 +1754,7 @@ __global__ void __launch_bounds__(kThreads, walk_min_blocks<APP, MODE, CLEAN, Of
       my_steps += (unsigned long long)k;
       if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
       else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+      if (HUBS != kHubOff && a.hub.fin) a.hub.fin[qi] = a.hub.fin_tag;
       st = 0u;
     }
   }
@@ -2060,6 +2064,7 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
       my_steps += (unsigned long long)k;
       if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
       else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+      if (a.hub.fin) a.hub.fin[qi] = a.hub.fin_tag;
     }
   }
   if (ring.failed) {
@@ -2276,6 +2281,7 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel_n2v(const 
       my_steps += (unsigned long long)k;
       if (a.hist_in_smem) atomicAdd(&s_hist[k], 1u);
       else atomicAdd(a.scratch + kSlotHist + k, 1ull);
+      if (a.hub.fin) a.hub.fin[qi] = a.hub.fin_tag;
     }
   }
   if (ring.failed) {
@@ -2425,6 +2431,84 @@ __global__ void hub_scatter_kernel(const int32_t* __restrict__ park_hub, const i
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int32_t h = park_hub[i];
     bucket[base[h] + atomicAdd(fill + h, 1u)] = park_qi[i];
+  }
+}
+
+// Early delivery of a hub-batched call's result.  The caller's walk table is page-locked host memory
+// the device can write (`host`, same layout as `result`).  Every walk that ends leaves the tag of its
+// launch in fin[query]; after each round of the series this kernel runs on a stream of its own and
+// copies the rows whose tag lies in (lo, hi] -- all of them written by launches that are complete --
+// to the host table while the next rounds walk on, so that the table's trip over PCIe (as long as
+// half a pass for 80-step walks) hides behind the walk instead of following it.  Tags above hi (walks
+// ending in launches that run beside this kernel) are left to a later launch; the last one takes
+// every tag left.  A warp looks at 128 queries at a time and copies four rows side by side, in
+// 128-byte segments aligned in the host table.  A few CTAs of 1,024 threads: what limits the kernel
+// is the round trip of its stores over PCIe, so it needs many warps in flight, and every SM it sits
+// on is one the walk kernels share (measured on config 2, whole call: 4 CTAs 79 ms -- delivery falls
+// behind --, 6 CTAs 63 ms, 8 CTAs 64-65 ms, 12 CTAs 67 ms, 32 CTAs of 256 threads 68 ms, one copy
+// after the last launch 76.5 ms).
+constexpr int kDeliverThreads = 1024;
+constexpr int kDeliverRows = 4;  // rows a warp copies side by side
+struct DeliverCtl {
+  unsigned int rows;  // rows that have been written to the host table by the launches so far
+  unsigned int stop;  // set by the host: the table will travel in one copy after all, give up
+};
+__global__ void __launch_bounds__(kDeliverThreads) deliver_kernel(const int32_t* __restrict__ result, int32_t* __restrict__ host,
+                                                                  const int32_t* fin, long long n, int D, int lo, int hi,
+                                                                  DeliverCtl* ctl) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int segs = (D + 31 + 31) / 32;  // segments of 32 cells a row can touch
+  for (long long base = warp * 128; base < n; base += warps * 128) {
+    if (ld_volatile(&ctl->stop) != 0u) return;
+    const long long q4 = base + 4 * (long long)lane;
+    int f[4] = {0, 0, 0, 0};
+    if (q4 + 3 < n) {
+      const int4 v = __ldcg(reinterpret_cast<const int4*>(fin + q4));
+      f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    } else {
+      for (int c = 0; c < 4; ++c) if (q4 + c < n) f[c] = __ldcg(fin + q4 + c);
+    }
+    // bit 4 l + c of the warp's 128-bit mask: query base + 4 l + c is to be delivered
+    uint32_t m[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) m[c] = __ballot_sync(0xFFFFFFFFu, f[c] > lo && f[c] <= hi);
+    const unsigned int found = __popc(m[0]) + __popc(m[1]) + __popc(m[2]) + __popc(m[3]);
+    int c = 0;
+    while (c < 4) {
+      long long o[kDeliverRows];
+      int z0[kDeliverRows];
+      int rows = 0;
+#pragma unroll
+      for (int r = 0; r < kDeliverRows; ++r) {
+        while (c < 4 && m[c] == 0u) ++c;
+        o[r] = -1; z0[r] = 0;
+        if (c < 4) {
+          const long long q = base + 4 * (long long)(__ffs((int)m[c]) - 1) + c;
+          m[c] &= m[c] - 1u;
+          o[r] = q * D;
+          z0[r] = (int)lane - (int)(((uintptr_t)(host + o[r]) >> 2) & 31u);
+          ++rows;
+        }
+      }
+      if (rows == 0) break;
+      for (int t = 0; t < segs; ++t) {
+        int32_t v[kDeliverRows];
+        bool u[kDeliverRows];
+#pragma unroll
+        for (int r = 0; r < kDeliverRows; ++r) {
+          const int z = z0[r] + 32 * t;
+          u[r] = o[r] >= 0 && z >= 0 && z < D;
+          v[r] = 0;
+          if (u[r]) v[r] = __ldcs(result + o[r] + z);
+        }
+#pragma unroll
+        for (int r = 0; r < kDeliverRows; ++r)
+          if (u[r]) host[o[r] + z0[r] + 32 * t] = v[r];
+      }
+    }
+    if (found != 0u && lane == 0) atomicAdd(&ctl->rows, found);
   }
 }
 

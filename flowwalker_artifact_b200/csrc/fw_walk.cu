@@ -52,6 +52,10 @@ static constexpr int64_t kHubPartSupers = 24;  // supergroups (49,152 neighbours
 static constexpr int64_t kHubMaxParts = 64;
 static constexpr int64_t kHubTailMin = 2048;   // parked walkers below which a call goes to its tail launch ...
 static constexpr int64_t kHubTailShare = 16;   // ... or below this share of the call's queries
+// CTAs (of 1,024 threads) of a deliver_kernel launch: as few as keep up with the walk (see deliver_kernel).
+static constexpr int kDeliverCtas = 8;
+static constexpr int kDeliverMinCells = 32;       // shortest result row (d + 1) early delivery takes on
+static constexpr double kLinkBytesPerUs = 50e3;   // what a walk table is assumed to need on the host link: 50 GB/s
 
 // Device control words of one round of a hub-batched call.
 struct HubCtl {
@@ -86,6 +90,13 @@ struct fw_engine {
   size_t scratch_words = 0;
   cudaStream_t stream = nullptr, stream2 = nullptr;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // early delivery of a hub-batched call's result into page-locked host memory (deliver_kernel)
+  int early_delivery = -1;         // -1: where the table is host memory the device can write and the walk is long
+                                   // enough, 0: never, 1: from the first launch on, 2: as 1 with the fallback copy
+  cudaStream_t stream_out = nullptr;
+  cudaEvent_t ev_round = nullptr;  // end of a round's launches on the walk stream
+  cudaEvent_t ev_out = nullptr;    // end of the last deliver_kernel launch of a call
+  int32_t* d_fin = nullptr;        // [hub_cap] tag of the launch each query's walk ended in
   // hub batching: the hub vertices and the buffers of a hub-batched call (grown on demand)
   int hub_mode = -1;           // -1: when it pays, 0: never, 1: whenever the graph has hubs, 2: as 1 without the tail launch
   struct HubSet {                  // the hub vertices for one limit
@@ -220,14 +231,15 @@ int ensure_hub_buffers(fw_engine* e, size_t n, size_t classes) {
   if (n <= e->hub_cap && (e->hub_cap / 32) * (size_t)kHubMaxParts + parts_total + 1 <= e->items_cap) return FW_OK;
   n = std::max(n, e->hub_cap);
   cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
-  cudaFree(e->d_best64); cudaFree(e->d_part_done);
+  cudaFree(e->d_best64); cudaFree(e->d_part_done); cudaFree(e->d_fin);
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_park_hub[i]); cudaFree(e->d_park_qi[i]); }
-  e->d_kstate = e->d_list = e->d_bucket = nullptr;
+  e->d_kstate = e->d_list = e->d_bucket = e->d_fin = nullptr;
   e->d_items = nullptr; e->d_best64 = nullptr; e->d_part_done = nullptr;
   e->d_park_hub[0] = e->d_park_hub[1] = e->d_park_qi[0] = e->d_park_qi[1] = nullptr;
   e->hub_cap = 0;
   const size_t cap = std::max<size_t>(n, 1024);
   FW_CUDA(cudaMalloc(&e->d_kstate, cap * 4));
+  FW_CUDA(cudaMalloc(&e->d_fin, cap * 4));
   FW_CUDA(cudaMalloc(&e->d_list, cap * 4));
   FW_CUDA(cudaMalloc(&e->d_bucket, cap * 4));
   for (int i = 0; i < 2; ++i) {
@@ -247,7 +259,10 @@ int ensure_hub_buffers(fw_engine* e, size_t n, size_t classes) {
 // rounds of plan, scatter, hub kernel, walk kernel while walkers are parked at hubs.  Every round
 // ends with the host reading the number of parked walkers, so this returns with the walk done.
 int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p, WalkArgs a, int64_t n,
-                    cudaStream_t st, size_t smem, int* launches) {
+                    cudaStream_t st, size_t smem, int32_t* host_table, bool* table_delivered, int* launches) {
+  *table_delivered = false;
+  // rows shorter than a 128-byte segment are not worth a warp each: such tables travel in one copy
+  if (p->d + 1 < kDeliverMinCells) host_table = nullptr;
   // MetaPath: walkers at the same step modulo the schema length want the same label and may share a sweep
   const int classes = p->app == FW_APP_METAPATH ? p->schema_len : 1;
   const size_t keys = (size_t)hs.n * (size_t)classes;
@@ -287,6 +302,64 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
   a.hub.kstate = e->d_kstate;
   a.hub.next_list = e->d_list; a.hub.bucket = e->d_bucket; a.hub.items = e->d_items;
   a.hub.hub_parts = d_parts; a.hub.best64 = e->d_best64; a.hub.part_done = e->d_part_done;
+  // Early delivery: rows of walks that ended up to the launches enqueued so far go to the caller's
+  // host table on a stream of their own, behind an event on the walk stream.  d_fin serves one call
+  // at a time: the walk stream waits for the previous call's last delivery before it clears it.
+  // The device's stores over PCIe are slower than the copy engine (45 against 57 GB/s alone, about
+  // 20 GB/s beside the walk kernels, which they slow by a tenth), so delivery pays only where the
+  // walk lasts about as long as the copy would: it begins once the series has run for a quarter of
+  // the time the table needs on the link (a call that is over before then copies the table in one
+  // piece, as without delivery), and a call that ends with less than a quarter of its rows delivered
+  // stops the launches in flight and copies the whole table as well.
+  int32_t tag = 0, delivered_to = 0;
+  bool delivering = false;
+  const int deliver_grid = [&] {
+    const char* env = getenv("FW_DELIVER_CTAS");  // development aid
+    return env && atoi(env) > 0 ? atoi(env) : kDeliverCtas;
+  }();
+  DeliverCtl* const dctl = reinterpret_cast<DeliverCtl*>(e->d_ctl + 2 * sizeof(HubCtl));
+  const double link_us = (double)n * (double)(p->d + 1) * 4.0 / kLinkBytesPerUs;
+  const auto t_begin = std::chrono::steady_clock::now();
+  if (host_table) {
+    FW_CUDA(cudaStreamWaitEvent(st, e->ev_out, 0));
+    FW_CUDA(cudaMemsetAsync(e->d_fin, 0, (size_t)n * 4, st));
+    FW_CUDA(cudaMemsetAsync(dctl, 0, sizeof(DeliverCtl), st));
+    a.hub.fin = e->d_fin;
+  }
+  // after the launches of a round have been enqueued
+  auto deliver = [&]() -> int {
+    if (!host_table) return FW_OK;
+    if (!delivering) {
+      const double us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_begin).count();
+      if (e->early_delivery < 1 && us < link_us / 4) return FW_OK;
+      delivering = true;
+    }
+    FW_CUDA(cudaEventRecord(e->ev_round, st));
+    FW_CUDA(cudaStreamWaitEvent(e->stream_out, e->ev_round, 0));
+    deliver_kernel<<<deliver_grid, kDeliverThreads, 0, e->stream_out>>>(a.result, host_table, e->d_fin, (long long)n, p->d + 1,
+                                                                         delivered_to, tag, dctl);
+    FW_CUDA(cudaGetLastError());
+    delivered_to = tag;
+    ++*launches;
+    return FW_OK;
+  };
+  // when the last launch of the series has returned: the rest of the table, one way or the other
+  auto finish_delivery = [&]() -> int {
+    if (!host_table || !delivering) return FW_OK;
+    FW_CUDA(cudaMemcpyAsync(e->h_ctl + 2, &dctl->rows, 4, cudaMemcpyDeviceToHost, st));
+    FW_CUDA(cudaStreamSynchronize(st));
+    if (e->early_delivery == 2 || (e->early_delivery < 1 && (int64_t)e->h_ctl[2] < n / 4)) {
+      FW_CUDA(cudaMemsetAsync(&dctl->stop, 0xFF, 4, st));
+    } else {
+      deliver_kernel<<<deliver_grid, kDeliverThreads, 0, e->stream_out>>>(a.result, host_table, e->d_fin, (long long)n, p->d + 1,
+                                                                           delivered_to, INT32_MAX, dctl);
+      FW_CUDA(cudaGetLastError());
+      ++*launches;
+      *table_delivered = true;
+    }
+    FW_CUDA(cudaEventRecord(e->ev_out, e->stream_out));  // the caller's stream waits for this one
+    return FW_OK;
+  };
   auto parks_into = [&](int set) {
     a.hub.park_hub = e->d_park_hub[set]; a.hub.park_qi = e->d_park_qi[set];
     a.hub.park_n = &ctl[set].park_n; a.hub.hub_cnt = hs.d_cnt + (size_t)set * keys;
@@ -300,8 +373,11 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
   {
     const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
     const int grid = (int)std::min<int64_t>(full_walk, std::max<int64_t>(want, 1));
+    a.hub.fin_tag = ++tag;
     FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(grid), dim3(kThreads), params, walk_smem, st));
     ++*launches;
+    rc = deliver();
+    if (rc) return rc;
   }
   const bool trace = getenv("FW_HUB_TRACE") != nullptr;  // development aid: the rounds on stderr
   const auto t_trace = std::chrono::steady_clock::now();
@@ -318,6 +394,7 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
     if (parked < tail_limit) {
       a.hub.list = e->d_park_qi[cur]; a.hub.list_n = &ctl[cur].park_n; a.hub.work = &ctl[cur].work_hub;
       const int tgrid = (int)std::min<int64_t>((int64_t)e->sms * tail_per_sm, std::max<int64_t>(((int64_t)parked + 31) / 32, 1));
+      a.hub.fin_tag = ++tag;
       FW_CUDA(cudaLaunchKernel((const void*)tail_fn, dim3(tgrid), dim3(kThreads), params, smem, st));
       ++*launches;
       // the engine's hub buffers serve one call at a time: the next one (a batch on the other
@@ -344,6 +421,7 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
     a.hub.list = nullptr; a.hub.list_n = nullptr;
     const int64_t max_items = ((int64_t)parked / 32) * kHubMaxParts + (int64_t)hs.parts_total * classes;
     const int hgrid = (int)std::min<int64_t>(full_hub, std::max<int64_t>((max_items + 7) / 8, 1));
+    a.hub.fin_tag = ++tag;
     FW_CUDA(cudaLaunchKernel((const void*)hub_fn, dim3(hgrid), dim3(kThreads), params, hub_smem, st));
     // walk kernel: the walkers the hub kernel listed
     a.hub.list = e->d_list; a.hub.list_n = &ctl[nxt].list_n; a.hub.work = &ctl[nxt].work_walk;
@@ -351,8 +429,28 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
     FW_CUDA(cudaLaunchKernel((const void*)walk_fn, dim3(wgrid), dim3(kThreads), params, walk_smem, st));
     *launches += 5;
     cur = nxt;
+    rc = deliver();
+    if (rc) return rc;
   }
-  return FW_OK;
+  return finish_delivery();
+}
+
+// The device's view of `bytes` of host memory at `host`, if all of it is page-locked memory the
+// device can address (cudaHostAlloc, cudaMallocHost, cudaHostRegister); nullptr otherwise.
+int32_t* device_view(const fw_engine* e, const void* host, size_t bytes) {
+  if (e->early_delivery == 0 || !host || bytes == 0) return nullptr;
+  const char* env = getenv("FLOWWALKER_EARLY_DELIVERY");
+  if (env && env[0] == '0') return nullptr;
+  cudaPointerAttributes first, last;
+  if (cudaPointerGetAttributes(&first, host) != cudaSuccess ||
+      cudaPointerGetAttributes(&last, static_cast<const char*>(host) + bytes - 1) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (first.type != cudaMemoryTypeHost || last.type != cudaMemoryTypeHost || !first.devicePointer || !last.devicePointer)
+    return nullptr;
+  if (static_cast<char*>(last.devicePointer) - static_cast<char*>(first.devicePointer) != (ptrdiff_t)(bytes - 1)) return nullptr;
+  return static_cast<int32_t*>(first.devicePointer);
 }
 
 // Enqueues: scratch reset, kernel(s) between ev_begin and ev_end, scratch read-back.  *launches
@@ -360,8 +458,10 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
 // when this returns; a single-kernel call is only enqueued.
 int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_dev, int64_t n,
                  int32_t* result_dev, cudaStream_t st, cudaEvent_t ev_begin, cudaEvent_t ev_end,
-                 unsigned long long* d_scratch, unsigned long long* h_scratch, int* launches) {
+                 unsigned long long* d_scratch, unsigned long long* h_scratch, int* launches,
+                 int32_t* host_table = nullptr, bool* delivered = nullptr) {
   *launches = 0;
+  if (delivered) *delivered = false;
   WalkArgs a;
   memset(&a.hub, 0, sizeof(a.hub));
   a.xadj = e->d_xadj; a.adj = e->d_adj; a.weight = e->d_weight; a.label = e->d_label;
@@ -400,8 +500,10 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
                     n < ((int64_t)1 << 31) &&
                     (int64_t)hs.n * (p->app == FW_APP_METAPATH ? p->schema_len : 1) <= (int64_t)kPlanMaxTiles * kPlanTile / 2;
   if (n > 0 && hubs) {
-    const int hrc = run_hub_batched(e, hs, p, a, n, st, smem, launches);
+    bool table_delivered = false;
+    const int hrc = run_hub_batched(e, hs, p, a, n, st, smem, host_table, &table_delivered, launches);
     if (hrc) return hrc;
+    if (delivered) *delivered = table_delivered;
   } else if (n > 0) {
     const int64_t want = (n + (kThreads / 32) * kMinClaim - 1) / ((kThreads / 32) * kMinClaim);
     const int grid = (int)std::min<int64_t>((int64_t)e->sms * per_sm, std::max<int64_t>(want, 1));
@@ -410,6 +512,7 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
     *launches = 1;
   }
   FW_CUDA(cudaEventRecord(ev_end, st));
+  if (host_table && n > 0 && hubs) FW_CUDA(cudaStreamWaitEvent(st, e->ev_out, 0));  // the table is complete when st is
   FW_CUDA(cudaMemcpyAsync(h_scratch, d_scratch, words * 8, cudaMemcpyDeviceToHost, st));
   return FW_OK;
 }
@@ -515,7 +618,7 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
     }
     if (e->hubset[0].n > 0 || e->hubset[1].n > 0) {
       FW_CUDA(cudaMalloc(&e->d_tile_tot, (size_t)kPlanMaxTiles * sizeof(uint2)));
-      FW_CUDA(cudaMalloc(&e->d_ctl, 2 * sizeof(HubCtl)));
+      FW_CUDA(cudaMalloc(&e->d_ctl, 2 * sizeof(HubCtl) + sizeof(DeliverCtl)));
       FW_CUDA(cudaMallocHost(&e->h_ctl, 64));
     }
     if (want_w && !g->weight) return fw::fail(FW_ERR_ARG, "graph has no weights");
@@ -535,6 +638,14 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
     FW_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
     FW_CUDA(cudaStreamCreateWithFlags(&e->stream2, cudaStreamNonBlocking));
     for (auto& ev : e->ev) FW_CUDA(cudaEventCreate(&ev));
+    {
+      // the delivery stream's few CTAs must not queue behind the walk kernels' full grids
+      int prio_low = 0, prio_high = 0;
+      FW_CUDA(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high));
+      FW_CUDA(cudaStreamCreateWithPriority(&e->stream_out, cudaStreamNonBlocking, prio_high));
+      FW_CUDA(cudaEventCreateWithFlags(&e->ev_round, cudaEventDisableTiming));
+      FW_CUDA(cudaEventCreateWithFlags(&e->ev_out, cudaEventDisableTiming));
+    }
     return ensure_scratch(e, 1023);
   };
   rc = body();
@@ -553,12 +664,15 @@ extern "C" void fw_engine_destroy(fw_engine* e) {
   cudaFree(e->d_ctl); cudaFree(e->d_tile_tot);
   if (e->h_ctl) cudaFreeHost(e->h_ctl);
   cudaFree(e->d_kstate); cudaFree(e->d_list); cudaFree(e->d_bucket); cudaFree(e->d_items);
-  cudaFree(e->d_best64); cudaFree(e->d_part_done);
+  cudaFree(e->d_best64); cudaFree(e->d_part_done); cudaFree(e->d_fin);
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_park_hub[i]); cudaFree(e->d_park_qi[i]); }
   for (int i = 0; i < 2; ++i) { cudaFree(e->d_starts[i]); cudaFree(e->d_result[i]); }
   if (e->stream) cudaStreamDestroy(e->stream);
   if (e->stream2) cudaStreamDestroy(e->stream2);
+  if (e->stream_out) cudaStreamDestroy(e->stream_out);
   for (auto& ev : e->ev) if (ev) cudaEventDestroy(ev);
+  if (e->ev_round) cudaEventDestroy(e->ev_round);
+  if (e->ev_out) cudaEventDestroy(e->ev_out);
   delete e;
 }
 
@@ -571,6 +685,12 @@ extern "C" int fw_engine_set_sharing(fw_engine* e, int mode) {
 extern "C" int fw_engine_set_hub_batching(fw_engine* e, int mode) {
   if (!e || mode < -1 || mode > 2) return fw::fail(FW_ERR_ARG, "fw_engine_set_hub_batching: mode must be -1, 0, 1 or 2");
   e->hub_mode = mode;
+  return FW_OK;
+}
+
+extern "C" int fw_engine_set_early_delivery(fw_engine* e, int mode) {
+  if (!e || mode < -1 || mode > 2) return fw::fail(FW_ERR_ARG, "fw_engine_set_early_delivery: mode must be -1, 0, 1 or 2");
+  e->early_delivery = mode;
   return FW_OK;
 }
 
@@ -629,9 +749,11 @@ extern "C" int fw_walk(fw_engine* e, const fw_walk_params* p, const int32_t* sta
   FW_CUDA(cudaEventRecord(e->ev[2], st));
   if (n > 0) FW_CUDA(cudaMemcpyAsync(e->d_starts[0], starts_host, (size_t)n * 4, cudaMemcpyHostToDevice, st));
   int launches = 0;
-  rc = enqueue_walk(e, p, e->d_starts[0], n, e->d_result[0], st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch, &launches);
+  bool delivered = false;
+  rc = enqueue_walk(e, p, e->d_starts[0], n, e->d_result[0], st, e->ev[0], e->ev[1], e->d_scratch, e->h_scratch, &launches,
+                    device_view(e, result_host, cells * 4), &delivered);
   if (rc) return rc;
-  if (n > 0) FW_CUDA(cudaMemcpyAsync(result_host, e->d_result[0], cells * 4, cudaMemcpyDeviceToHost, st));
+  if (n > 0 && !delivered) FW_CUDA(cudaMemcpyAsync(result_host, e->d_result[0], cells * 4, cudaMemcpyDeviceToHost, st));
   FW_CUDA(cudaEventRecord(e->ev[3], st));
   FW_CUDA(cudaStreamSynchronize(st));
   float ms = 0.f, total = 0.f;
@@ -669,7 +791,7 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
   const size_t words = (size_t)kSlotHist + D;
   rc = ensure_scratch(e, (int)(2 * words));
   if (rc) return rc;
-  auto bail = [&](int code) { cudaStreamSynchronize(e->stream); cudaStreamSynchronize(e->stream2); return code; };
+  auto bail = [&](int code) { cudaStreamSynchronize(e->stream); cudaStreamSynchronize(e->stream2); cudaStreamSynchronize(e->stream_out); return code; };
   for (int i = 0; i < 2; ++i) {
     rc = ensure_cap(&e->d_starts[i], &e->cap_starts[i], (size_t)batch_size);
     if (!rc) rc = ensure_cap(&e->d_result[i], &e->cap_result[i], (size_t)batch_size * D);
@@ -682,6 +804,7 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
   if (stats) { stats->steps = 0; stats->scanned = 0; stats->device_ms = 0; stats->total_ms = 0; stats->device_status = 0; stats->launches = 0; }
   if (len_hist) for (size_t z = 0; z < D; ++z) len_hist[z] = 0;
   cudaEvent_t t0 = e->ev[4], t1 = e->ev[5];
+  int32_t* const table_dev = device_view(e, pinned, (size_t)n * D * 4);  // early delivery, where the table allows it
   cudaEventRecord(t0, streams[0]);
   bool pending[2] = {false, false};
   int batch_launches[2] = {0, 0};
@@ -703,10 +826,12 @@ static int walk_batches(fw_engine* e, const fw_walk_params* p, const int32_t* st
     bp.query_id_base = p->query_id_base + (uint64_t)off * (p->query_id_stride ? p->query_id_stride : 1);
     cudaError_t err = cudaMemcpyAsync(e->d_starts[which], starts_host + off, (size_t)m * 4, cudaMemcpyHostToDevice, st);
     if (err != cudaSuccess) { rc = fw::fail(FW_ERR_CUDA, "H2D copy failed: %s", cudaGetErrorString(err)); break; }
+    bool delivered = false;
     rc = enqueue_walk(e, &bp, e->d_starts[which], m, e->d_result[which], st, evs[which][0], evs[which][1], dsc[which], hsc[which],
-                      &batch_launches[which]);
+                      &batch_launches[which], table_dev ? table_dev + (size_t)off * D : nullptr, &delivered);
     if (rc) break;
-    err = cudaMemcpyAsync(pinned + (size_t)off * D, e->d_result[which], (size_t)m * D * 4, cudaMemcpyDeviceToHost, st);
+    err = delivered ? cudaSuccess
+                    : cudaMemcpyAsync(pinned + (size_t)off * D, e->d_result[which], (size_t)m * D * 4, cudaMemcpyDeviceToHost, st);
     if (err != cudaSuccess) { rc = fw::fail(FW_ERR_CUDA, "D2H copy failed: %s", cudaGetErrorString(err)); break; }
     pending[which] = true;
   }

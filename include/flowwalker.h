@@ -163,6 +163,21 @@ int fw_engine_set_sharing(fw_engine* e, int mode);
  * of a call are walked to the end by one launch without batching).
  * Results do not depend on it. */
 int fw_engine_set_hub_batching(fw_engine* e, int mode);
+/* Early delivery of the walk table (the role of the reference's overlap of walking and copying in
+ * walk_batch, src/walk.cu:373-466, inside one call): when the result buffer of fw_walk,
+ * fw_walk_batch or fw_walk_batch_into is page-locked host memory the device can address
+ * (cudaHostAlloc, cudaMallocHost, cudaHostRegister; fw_walk_batch's own buffer always is), the
+ * call is hub-batched and a result row has at least 32 cells, the rows of walks that have ended
+ * are written to it by a small kernel on a stream of its own while the remaining walkers walk on,
+ * instead of one copy of the whole table after the last launch.
+ * mode -1 (default): delivery begins once the call has run for a quarter of the time its table
+ * needs on the host link, so a call whose walk is short beside its copy never delivers, and a call
+ * that ends with less than a quarter of its rows delivered stops delivering and copies the table
+ * in one piece; 0: never (one copy at the end); 1: from the first launch on, to the last row;
+ * 2: from the first launch on, then always the fallback copy (1 and 2 exist for tests).
+ * The environment variable FLOWWALKER_EARLY_DELIVERY=0 has the effect of mode 0.
+ * Results do not depend on it. */
+int fw_engine_set_early_delivery(fw_engine* e, int mode);
 /* Number of hub vertices of the engine's graph and the row length from which a vertex is one,
  * for the two limits a call chooses from (which = 0: 1,016 neighbours, 1: 504; the lower one
  * serves calls that bring at least a hundred queries per hub). */

@@ -127,6 +127,72 @@ def test_hub_batching_on_and_off(app, kw, hub):
 
 
 @pytest.mark.parametrize("app,kw", APPS)
+def test_early_delivery_into_page_locked_memory(app, kw):
+    """A hub-batched call whose result buffer is page-locked host memory may write the rows of
+    ended walks to it round by round (deliver_kernel on a stream of its own) instead of copying the
+    table after the last launch.  Same table every way, and the golden walker's: delivery to the
+    last row (mode 1), delivery stopped and the table copied after all (mode 2), the engine's own
+    choice (-1), no delivery (0); one batch and several (rows of the later batches start anywhere
+    in the host table), the callee's buffer (fw_walk_batch), a caller's page-locked buffer at an
+    odd offset (fw_walk_batch_into, fw_walk), pageable memory (nothing to deliver to), and rows too
+    short to be delivered (MetaPath's 6 cells)."""
+    import torch
+    cases = []
+    arrs = graphs.ragged()
+    cases.append((arrs, np.concatenate([np.arange(arrs["n_rows"])] * 3).astype(np.int32), 33))
+    star = graphs.star()
+    star["label"][:100000] = np.arange(100000) % 5
+    starts = np.zeros(3000, dtype=np.int32)
+    starts[1::3] = np.arange(1, 3000, 3) % 1000 + 1
+    cases.append((star, starts, 31))
+    r = fw.rmat(16, 16 << 16, weight_range=(0.0, 1.0), n_labels=5)
+    cases.append((dict(xadj=r.xadj.copy(), adj=r.adj.copy(), weight=r.weight.copy(), label=r.label.copy()),
+                  np.arange(r.V, dtype=np.int32), 40))
+    for arrs, starts, d in cases:
+        kw2 = dict(kw, d=d if app != fw.APP_METAPATH else kw["d"])
+        n, D = len(starts), kw2["d"] + 1
+        g = fw.Graph.from_arrays(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"])
+        eng = fw.Engine(g, 0)
+        eng.set_hub_batching(1)
+        prm = fw.make_params(app, seed=31, query_id_base=5, **kw2)
+        ref, steps, _, _ = O.walk(arrs["xadj"], arrs["adj"], arrs["weight"], arrs["label"], app, starts,
+                                  seed=31, query_id_base=5, **kw2)
+        launches = {}
+        for mode in (1, 2, -1, 0):
+            eng.set_early_delivery(mode)
+            out, st = eng.walk_batch(prm, starts, batch_size=n)
+            assert (out == ref).all() and st.steps == steps and st.device_status == 0
+            launches[mode] = st.launches
+            out, st = eng.walk_batch(prm, starts, batch_size=max(n // 3 - 7, 1))
+            assert (out == ref).all() and st.steps == steps
+            # a caller's page-locked buffer, the table 12 bytes off its start
+            flat = torch.full((n * D + 8,), -9, dtype=torch.int32).pin_memory()
+            table = flat[3:3 + n * D]
+            st2 = fw.WalkStats()
+            assert fw.lib().fw_walk_batch_into(eng._h, prm[0], starts.ctypes.data, n, n, 512, table.data_ptr(), st2, None) == 0
+            assert (table.numpy().reshape(n, D) == ref).all()
+            assert flat[:3].tolist() == [-9] * 3 and flat[3 + n * D:].tolist() == [-9] * 5
+            flat.fill_(-9)
+            st3 = fw.WalkStats()
+            assert fw.lib().fw_walk(eng._h, prm[0], starts.ctypes.data, n, table.data_ptr(), st3, None) == 0
+            assert (table.numpy().reshape(n, D) == ref).all()
+            assert flat[:3].tolist() == [-9] * 3 and flat[3 + n * D:].tolist() == [-9] * 5
+            if mode in (0, 1, 2):  # the engine's own choice depends on the clock
+                assert st2.launches == launches[mode] and st3.launches == launches[mode]
+        if D >= 32:  # the delivery launches are counted: one per round, and one more for the last rows
+            assert launches[1] == launches[2] + 1 and launches[2] > launches[0] > 1
+        else:
+            assert launches[1] == launches[2] == launches[0] > 1
+        assert launches[0] <= launches[-1] <= launches[1]
+        # pageable memory: nothing the device could write to, one copy at the end
+        eng.set_early_delivery(1)
+        out, st = eng.walk(prm, starts)
+        assert (out == ref).all() and st.launches == launches[0]
+        eng.close()
+        g.close()
+
+
+@pytest.mark.parametrize("app,kw", APPS)
 def test_rmat16_many_queries(app, kw):
     g = fw.rmat(16, 16 << 16, weight_range=(0.0, 1.0), n_labels=5)
     arrs = dict(xadj=g.xadj.copy(), adj=g.adj.copy(), weight=g.weight.copy(), label=g.label.copy())
