@@ -140,6 +140,12 @@ class ClockSampler:
 # was captured on; a line measured on another revision, or on a workload without an entry, reports
 # traffic = null with the reason.
 PROFILED = {
+    ("deepwalk", 22, 16, 80, 64): {
+        "kernel_revision": "hub-batched-3",
+        "captured_on": "2,700,000-query call on the same graph (profiles/hub_batched_pass_deepwalk_scale22.md)",
+        "dram_per_algorithmic_byte": 0.0606, "issue_active": 0.626, "l2_hit_rate": 0.476,
+        "instructions_per_step": 317.9,
+    },
 }
 
 
@@ -576,6 +582,7 @@ def main():
                          ", scaled by algorithmic bytes",
                          "dram_frac": traffic / (per_launch_ms * 1e-3) / 1e9 / peak,
                          "issue_active": prof["issue_active"], "l2_hit_rate": prof["l2_hit_rate"],
+                         "warp_instructions_per_step": prof["instructions_per_step"],
                          "limited_by": "instruction issue and latency, not HBM: shared sweeps and L2-resident hub rows keep "
                                        "DRAM traffic far below the algorithmic bytes, so frac exceeds 1"})
         else:

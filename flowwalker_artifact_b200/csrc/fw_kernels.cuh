@@ -20,7 +20,7 @@
 namespace fwk {
 
 // Bumped with every change of the device code that can move its counters.
-#define FW_KERNEL_REVISION "hub-batched-2"
+#define FW_KERNEL_REVISION "hub-batched-3"
 
 constexpr int kMaxSchema = 64;
 constexpr int kWarpsPerCta = 8;
@@ -1420,10 +1420,19 @@ __device__ __forceinline__ int32_t hub_index(const int32_t* __restrict__ ids, in
   return lo;
 }
 
+// One slot each of a list for the lanes that call this together: one atomic for all of them.
+__device__ __forceinline__ uint32_t claim_slot(uint32_t* counter) {
+  const uint32_t act = __activemask(), lane = threadIdx.x & 31u;
+  const int leader = __ffs((int)act) - 1;
+  uint32_t first = 0;
+  if ((int)lane == leader) first = atomicAdd(counter, (uint32_t)__popc(act));
+  return __shfl_sync(act, first, leader) + (uint32_t)__popc(act & ((1u << lane) - 1u));
+}
+
 // A walker that arrived at a hub vertex `cur` after k steps waits there for the next hub launch.
 __device__ __forceinline__ void hub_park(const HubArgs& hb, long long qi, int32_t k, int32_t cur) {
   const int32_t h = hub_index(hb.hub_ids, hb.n_hubs, cur) * hb.classes + (hb.classes > 1 ? k % hb.classes : 0);
-  const uint32_t pos = atomicAdd(hb.park_n, 1u);
+  const uint32_t pos = claim_slot(hb.park_n);
   hb.park_hub[pos] = h;
   hb.park_qi[pos] = (int32_t)qi;
   hb.kstate[qi] = k;
@@ -2044,7 +2053,7 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel(const __gr
             } else if ((uint64_t)(ne - nb) >= (uint64_t)a.hub.min_degree) {
               hub_park(a.hub, qi, k, nxt);
             } else {
-              const uint32_t pos = atomicAdd(a.hub.next_n, 1u);
+              const uint32_t pos = claim_slot(a.hub.next_n);
               a.hub.next_list[pos] = (int32_t)qi;
               a.hub.kstate[qi] = k;
             }
@@ -2262,7 +2271,7 @@ __global__ void __launch_bounds__(kThreads, FW_MIN_BLOCKS) hub_kernel_n2v(const 
             } else if ((uint64_t)(ne - nb) >= (uint64_t)a.hub.min_degree) {
               hub_park(a.hub, qi, k, nxt);
             } else {
-              const uint32_t pos = atomicAdd(a.hub.next_n, 1u);
+              const uint32_t pos = claim_slot(a.hub.next_n);
               a.hub.next_list[pos] = (int32_t)qi;
               a.hub.kstate[qi] = k;
             }
@@ -2391,7 +2400,13 @@ __global__ void __launch_bounds__(kPlanThreads) hub_plan_emit(uint32_t* cnt, uin
                                                               const uint16_t* __restrict__ parts, uint32_t* part_done, int n_keys,
                                                               int classes, const uint2* __restrict__ tile_off) {
   __shared__ uint32_t s_wc[32], s_wb[32], s_tot[2];
+  // keys with many batches: their items are written by a warp each, its lanes side by side (one
+  // thread would take as long as the rest of the round's planning together for the busiest hubs)
+  // (and the few keys with thousands of batches by the whole CTA)
+  constexpr uint32_t kBigGroups = 64, kBigCap = 1024, kHugeGroups = 2048, kHugeCap = 32;
+  __shared__ uint32_t s_big_n, s_big[kBigCap][5], s_huge_n, s_huge[kHugeCap][5];
   const int t = threadIdx.x, k0 = blockIdx.x * kPlanTile + t * kPlanKeys;
+  if (t == 0) { s_big_n = 0u; s_huge_n = 0u; }
   uint32_t n[kPlanKeys], np[kPlanKeys], my_c = 0, my_b = 0;
 #pragma unroll
   for (int i = 0; i < kPlanKeys; ++i) {
@@ -2412,16 +2427,49 @@ __global__ void __launch_bounds__(kPlanThreads) hub_plan_emit(uint32_t* cnt, uin
   for (int i = 0; i < kPlanKeys; ++i)
     if (k0 + i < n_keys) {
       base[k0 + i] = at;
-      for (uint32_t off = 0; off < n[i]; off += 32u) {
-        const uint32_t group = it;
-        part_done[group] = 0u;
-        for (uint32_t p = 0; p < np[i]; ++p)
-          items[it++] = make_int4(k0 + i, (int)(at + off), (int)(min(32u, n[i] - off) | (p << 8) | (np[i] << 16)), (int)group);
+      const uint32_t groups = (n[i] + 31u) >> 5;
+      uint32_t slot = kBigCap, hslot = kHugeCap;
+      if (groups > kHugeGroups) hslot = atomicAdd(&s_huge_n, 1u);
+      if (hslot >= kHugeCap && groups > kBigGroups) slot = atomicAdd(&s_big_n, 1u);
+      if (hslot < kHugeCap) {
+        s_huge[hslot][0] = (uint32_t)(k0 + i); s_huge[hslot][1] = n[i]; s_huge[hslot][2] = np[i]; s_huge[hslot][3] = at; s_huge[hslot][4] = it;
+        it += groups * np[i];
+      } else if (slot < kBigCap) {
+        s_big[slot][0] = (uint32_t)(k0 + i); s_big[slot][1] = n[i]; s_big[slot][2] = np[i]; s_big[slot][3] = at; s_big[slot][4] = it;
+        it += groups * np[i];
+      } else {
+        for (uint32_t off = 0; off < n[i]; off += 32u) {
+          const uint32_t group = it;
+          part_done[group] = 0u;
+          for (uint32_t p = 0; p < np[i]; ++p)
+            items[it++] = make_int4(k0 + i, (int)(at + off), (int)(min(32u, n[i] - off) | (p << 8) | (np[i] << 16)), (int)group);
+        }
       }
       at += n[i];
       if (n[i] != 0u) cnt[k0 + i] = 0u;
       fill[k0 + i] = 0u;
     }
+  __syncthreads();
+  const uint32_t huge = min(s_huge_n, kHugeCap);
+  for (uint32_t e = 0; e < huge; ++e) {
+    const uint32_t key = s_huge[e][0], kn = s_huge[e][1], knp = s_huge[e][2], kat = s_huge[e][3], kit = s_huge[e][4];
+    const uint32_t work = ((kn + 31u) >> 5) * knp;  // one item per thread and turn
+    for (uint32_t w = (uint32_t)t; w < work; w += kPlanThreads) {
+      const uint32_t j = w / knp, p = w - j * knp, group = kit + j * knp, off = 32u * j;
+      if (p == 0u) part_done[group] = 0u;
+      items[group + p] = make_int4((int)key, (int)(kat + off), (int)(min(32u, kn - off) | (p << 8) | (knp << 16)), (int)group);
+    }
+  }
+  const uint32_t big = min(s_big_n, kBigCap);
+  for (uint32_t e = (uint32_t)t >> 5; e < big; e += kPlanThreads / 32) {
+    const uint32_t key = s_big[e][0], kn = s_big[e][1], knp = s_big[e][2], kat = s_big[e][3], kit = s_big[e][4];
+    for (uint32_t j = (uint32_t)t & 31u; j < (kn + 31u) >> 5; j += 32u) {
+      const uint32_t group = kit + j * knp, off = 32u * j;
+      part_done[group] = 0u;
+      for (uint32_t p = 0; p < knp; ++p)
+        items[group + p] = make_int4((int)key, (int)(kat + off), (int)(min(32u, kn - off) | (p << 8) | (knp << 16)), (int)group);
+    }
+  }
 }
 
 __global__ void hub_scatter_kernel(const int32_t* __restrict__ park_hub, const int32_t* __restrict__ park_qi,
