@@ -39,14 +39,16 @@ static constexpr int64_t kSharingAutoDegree = 262144;
 // Hub batching: vertices of at least this many neighbours are hubs (about the reference's limit
 // between its warp and its block sampler, 1,024: include/walker.cuh:29).
 // A call uses the lower hub limit when it brings at least this many queries per hub of that limit
-// (measured: R-MAT scale 22, all-vertex queries, 168 per hub: 57 ms against 61 with the higher limit;
-// scale 24, 10^7 PPR queries, about 50 per hub: 31 ms against 24).
+// (measured on R-MAT scale 22, 19,324 hubs of the lower limit and 9,109 of the higher: 2,097,152
+// queries, 108 per hub, 31.4 ms against 32.6 with the higher limit; 1,048,576 queries 21.2 against
+// 20.5; scale 24, 10^7 PPR queries, about 50 per hub: 31 ms against 24).
 static constexpr int64_t kHubDenseQueries = 100;
 // A call is hub-batched at all when it brings at least this many queries per hub of the higher
 // limit: every round of the series has a fixed cost (its launches, the longest single sweep, one
 // read-back), which a short call does not earn back (R-MAT scale 22: 524,288 queries, 57 per hub,
-// take 15 ms either way; 10^6, 110 per hub, 23.4 ms batched against 24.0).
-static constexpr int64_t kHubMinQueries = 128;
+// take 15.0 ms batched and 15.2 in one launch; 1,048,576, 115 per hub, 20.5 ms against 27.8;
+// 2,097,152 31.4 against 53.3; 262,144 12.5 batched).
+static constexpr int64_t kHubMinQueries = 64;
 static constexpr int64_t kHubMax = (int64_t)1 << 22;
 static constexpr int64_t kHubPartSupers = 24;  // supergroups (49,152 neighbours) of a hub's row per sweeping warp, about
 static constexpr int64_t kHubMaxParts = 64;
@@ -495,7 +497,7 @@ int enqueue_walk(fw_engine* e, const fw_walk_params* p, const int32_t* starts_de
   // (node2vec: the higher limit always; its walk kernel stages nothing)
   fw_engine::HubSet& hs = (p->app != FW_APP_NODE2VEC && e->hubset[1].n > 0 && n >= kHubDenseQueries * e->hubset[1].n)
                               ? e->hubset[1] : e->hubset[0];
-  const bool worth_it = e->hub_mode > 0 || n >= kHubMinQueries * (int64_t)hs.n;
+  const bool worth_it = e->hub_mode > 0 || n >= kHubMinQueries * (int64_t)e->hubset[0].n;
   const bool hubs = e->hub_mode != 0 && worth_it && hs.n > 0 && mode == FW_GROUP_STRIP && e->sharing <= 0 &&
                     n < ((int64_t)1 << 31) &&
                     (int64_t)hs.n * (p->app == FW_APP_METAPATH ? p->schema_len : 1) <= (int64_t)kPlanMaxTiles * kPlanTile / 2;

@@ -158,7 +158,7 @@ int fw_engine_set_sharing(fw_engine* e, int mode);
  * wait there, and one sweep of the hub's row serves up to 32 of them.
  * DeepWalk and PPR with the strip sampler; a walk call then is a series of kernel launches.
  * mode -1 (default): on when the graph has such vertices and the call brings enough queries per
- * hub to earn back the fixed cost of the series (128 or more); 0: off; 1: on whenever the graph
+ * hub of 1,016 neighbours or more to earn back the fixed cost of the series (64 or more); 0: off; 1: on whenever the graph
  * has hubs; 2: as 1, and batching down to the last walker (by default the last few parked walkers
  * of a call are walked to the end by one launch without batching).
  * Results do not depend on it. */
