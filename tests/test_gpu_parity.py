@@ -188,6 +188,17 @@ def test_early_delivery_into_page_locked_memory(app, kw):
         eng.set_early_delivery(1)
         out, st = eng.walk(prm, starts)
         assert (out == ref).all() and st.launches == launches[0]
+        # the same pageable array page-locked by the caller (cudaHostRegister): delivered to if the
+        # device can address it, copied to otherwise; the same table either way
+        own = np.full((n, D), -9, dtype=np.int32)
+        rt = torch.cuda.cudart()
+        assert int(rt.cudaHostRegister(own.ctypes.data, own.nbytes, 0)) == 0
+        try:
+            st4 = fw.WalkStats()
+            assert fw.lib().fw_walk(eng._h, prm[0], starts.ctypes.data, n, own.ctypes.data, st4, None) == 0
+            assert (own == ref).all() and st4.launches in (launches[0], launches[1])
+        finally:
+            rt.cudaHostUnregister(own.ctypes.data)
         eng.close()
         g.close()
 
