@@ -52,8 +52,13 @@ static constexpr int64_t kHubMinQueries = 64;
 static constexpr int64_t kHubMax = (int64_t)1 << 22;
 static constexpr int64_t kHubPartSupers = 24;  // supergroups (49,152 neighbours) of a hub's row per sweeping warp, about
 static constexpr int64_t kHubMaxParts = 64;
-static constexpr int64_t kHubTailMin = 2048;   // parked walkers below which a call goes to its tail launch ...
-static constexpr int64_t kHubTailShare = 16;   // ... or below this share of the call's queries
+// A call goes to its tail launch when the walkers left parked would, sweeping alone, scan fewer than
+// this many neighbours in their next hub step (parked x mean row length of a hub): about what two
+// rounds cost in launches and read-backs.  Measured, ms per pass at 2e8 / 4e8-5e8 / 1e9 and with the
+// earlier rule of a sixteenth of the queries: config 2 52.0 / 52.1 / 53.1 / 52.0; PPR on the same
+// graph 6.07 / 6.09 / 6.35 / 5.93; config 3 20.96 / 20.42 / 21.56 / 25.25; config 5 61.2 / 61.2 / 61.2 / 65.9.
+static constexpr double kHubTailEdges = 4e8;
+static constexpr int64_t kHubTailMin = 2048;   // ... always once fewer than this many are left, never with a quarter of the queries or more
 // CTAs (of 1,024 threads) of a deliver_kernel launch: as few as keep up with the walk (see deliver_kernel).
 static constexpr int kDeliverCtas = 8;
 static constexpr int kDeliverMinCells = 32;       // shortest result row (d + 1) early delivery takes on
@@ -112,6 +117,8 @@ struct fw_engine {
     uint16_t* d_parts = nullptr;   // [n] parts the sweep of a hub's row is split into
     uint16_t* d_ones = nullptr;    // [n] the same for node2vec, whose hub kernel does not split rows
     uint64_t parts_total = 0;      // their sum
+    double mean_degree = 0;        // row length of a hub: plain mean, and mean over the edges (what a
+    double visit_degree = 0;       // walker that arrives by a uniformly drawn edge finds)
   } hubset[2];                     // 0: limit 1,016, 1: limit 504
   size_t hub_cap = 0;              // queries the buffers below are sized for
   int32_t* d_kstate = nullptr;
@@ -294,9 +301,10 @@ int run_hub_batched(fw_engine* e, fw_engine::HubSet& hs, const fw_walk_params* p
   if (rc) return rc;
   // Below this many parked walkers the batches are mostly empty and a round costs more than it
   // serves: the walkers left are then walked to the end by one launch, each sweeping for itself.
-  const char* ts_env = getenv("FW_HUB_TAIL_SHARE");  // development aid
-  const int64_t tail_share = ts_env && atoll(ts_env) > 0 ? atoll(ts_env) : kHubTailShare;
-  const uint32_t tail_limit = e->hub_mode == 2 ? 0u : (uint32_t)std::max<int64_t>(kHubTailMin, n / tail_share);
+  const char* te_env = getenv("FW_HUB_TAIL_EDGES");  // development aid
+  const double tail_edges = te_env && atof(te_env) > 0 ? atof(te_env) : kHubTailEdges;
+  const uint32_t tail_limit = e->hub_mode == 2 ? 0u
+      : (uint32_t)std::max<double>((double)kHubTailMin, std::min<double>(tail_edges / hs.mean_degree, (double)n / 4));
   HubCtl* ctl = reinterpret_cast<HubCtl*>(e->d_ctl);
   FW_CUDA(cudaMemsetAsync(e->d_ctl, 0, 2 * sizeof(HubCtl), st));
   FW_CUDA(cudaMemsetAsync(hs.d_cnt, 0, keys * 8, st));
@@ -602,14 +610,18 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
       if (ids.empty() || (int64_t)ids.size() > kHubMax) continue;
       // rows of more than kHubPartSupers supergroups are swept by several warps, a part each
       std::vector<uint16_t> parts(ids.size());
+      double sum_len = 0, sum_len2 = 0;
       for (size_t i = 0; i < ids.size(); ++i) {
         const int64_t b = fw::row_begin(g, ids[i]), len = fw::row_begin(g, (int64_t)ids[i] + 1) - b;
+        sum_len += (double)len; sum_len2 += (double)len * (double)len;
         const int64_t nq = ((b & 3) + len + 3) >> 2, n_half = (nq + kHalfQuads - 1) / kHalfQuads, supers = (n_half + 1) >> 1;
         parts[i] = (uint16_t)std::min<int64_t>(kHubMaxParts, (supers + part_supers - 1) / part_supers);
         hs.parts_total += parts[i];
       }
       hs.n = (int32_t)ids.size();
       hs.limit = (uint32_t)limit;
+      hs.mean_degree = sum_len / (double)ids.size();
+      hs.visit_degree = sum_len2 / sum_len;
       FW_CUDA(cudaMalloc(&hs.d_ids, ids.size() * 4));
       FW_CUDA(cudaMemcpy(hs.d_ids, ids.data(), ids.size() * 4, cudaMemcpyHostToDevice));
       FW_CUDA(cudaMalloc(&hs.d_parts, parts.size() * 2));
