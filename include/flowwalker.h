@@ -156,11 +156,13 @@ int fw_engine_set_sharing(fw_engine* e, int mode);
  * the degree-binned dispatch of include/walker.cuh:1357-1419): walkers that arrive at a vertex of
  * about a thousand neighbours or more (1,016; 504 in calls with many queries per such vertex)
  * wait there, and one sweep of the hub's row serves up to 32 of them.
- * DeepWalk and PPR with the strip sampler; a walk call then is a series of kernel launches.
+ * All four applications with the strip sampler (MetaPath: walkers that want the same label share;
+ * node2vec: the sweep of plain weights is shared, every walker's bias test is its own); a walk
+ * call then is a series of kernel launches.
  * mode -1 (default): on when the graph has such vertices and the call brings enough queries per
- * hub of 1,016 neighbours or more to earn back the fixed cost of the series (64 or more); 0: off; 1: on whenever the graph
- * has hubs; 2: as 1, and batching down to the last walker (by default the last few parked walkers
- * of a call are walked to the end by one launch without batching).
+ * hub of 1,016 neighbours or more to earn back the fixed cost of the series (64 or more); 0: off;
+ * 1: on whenever the graph has hubs; 2: as 1, and batching down to the last walker (by default
+ * the last parked walkers of a call are walked to the end by one launch without batching).
  * Results do not depend on it. */
 int fw_engine_set_hub_batching(fw_engine* e, int mode);
 /* Early delivery of the walk table (the role of the reference's overlap of walking and copying in
