@@ -26,6 +26,24 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(L, nm), "libflowwalker.so does not export " + nm
 
 
+def test_bench_profile_table_names_the_built_kernels(monkeypatch):
+    """bench.py reports DRAM traffic only from an ncu capture of the kernel revision it runs: the
+    bench workload's entry has to name the revision the library was built from, or the bench line
+    would carry traffic = null."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("fw_bench", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    entry = bench.PROFILED[("deepwalk", 22, 16, 80, 64)]
+    assert entry["kernel_revision"] == fw.lib().fw_kernel_revision().decode()
+    assert 0 < entry["dram_per_algorithmic_byte"] < 1 and 0 < entry["issue_active"] <= 1
+    import sys
+    monkeypatch.setattr(sys, "argv", ["bench.py"])
+    args = bench.parse()  # the default workload is the one the table's entry is keyed by
+    assert (args.app, args.scale, args.edge_factor, args.d, args.group or 64) == ("deepwalk", 22, 16, 80, 64)
+    assert (args.gpus, args.steps >= 3, args.warmup >= 3) == (1, True, True)
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     import flowwalker_artifact_b200._binding as B
     monkeypatch.setattr(B, "_lib", None)
