@@ -117,8 +117,7 @@ struct fw_engine {
     uint16_t* d_parts = nullptr;   // [n] parts the sweep of a hub's row is split into
     uint16_t* d_ones = nullptr;    // [n] the same for node2vec, whose hub kernel does not split rows
     uint64_t parts_total = 0;      // their sum
-    double mean_degree = 0;        // row length of a hub: plain mean, and mean over the edges (what a
-    double visit_degree = 0;       // walker that arrives by a uniformly drawn edge finds)
+    double mean_degree = 0;        // mean row length of a hub
   } hubset[2];                     // 0: limit 1,016, 1: limit 504
   size_t hub_cap = 0;              // queries the buffers below are sized for
   int32_t* d_kstate = nullptr;
@@ -610,10 +609,10 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
       if (ids.empty() || (int64_t)ids.size() > kHubMax) continue;
       // rows of more than kHubPartSupers supergroups are swept by several warps, a part each
       std::vector<uint16_t> parts(ids.size());
-      double sum_len = 0, sum_len2 = 0;
+      double sum_len = 0;
       for (size_t i = 0; i < ids.size(); ++i) {
         const int64_t b = fw::row_begin(g, ids[i]), len = fw::row_begin(g, (int64_t)ids[i] + 1) - b;
-        sum_len += (double)len; sum_len2 += (double)len * (double)len;
+        sum_len += (double)len;
         const int64_t nq = ((b & 3) + len + 3) >> 2, n_half = (nq + kHalfQuads - 1) / kHalfQuads, supers = (n_half + 1) >> 1;
         parts[i] = (uint16_t)std::min<int64_t>(kHubMaxParts, (supers + part_supers - 1) / part_supers);
         hs.parts_total += parts[i];
@@ -621,7 +620,6 @@ extern "C" int fw_engine_create(const fw_graph* g, int device, int which, fw_eng
       hs.n = (int32_t)ids.size();
       hs.limit = (uint32_t)limit;
       hs.mean_degree = sum_len / (double)ids.size();
-      hs.visit_degree = sum_len2 / sum_len;
       FW_CUDA(cudaMalloc(&hs.d_ids, ids.size() * 4));
       FW_CUDA(cudaMemcpy(hs.d_ids, ids.data(), ids.size() * 4, cudaMemcpyHostToDevice));
       FW_CUDA(cudaMalloc(&hs.d_parts, parts.size() * 2));
